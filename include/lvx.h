@@ -1,0 +1,127 @@
+/* lvx.h -- C ABI of liblvx.so: the sm_100a kernels behind lv_xattn's distributed cross-attention.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the CUDA stream it is given
+ * (a cudaStream_t passed as void*), never synchronises the host, and returns an int:
+ *    0   success
+ *   <0   invalid argument (nothing was launched); lvx_last_error() says which
+ *   >0   CUDA runtime / driver error code of the failing call
+ * No C++ exception crosses this boundary. The library keeps no device memory of its own except
+ * where an entry point says so; workspaces are supplied by the caller (sizes from
+ * lvx_query_workspace).
+ *
+ * Each declaration names the part of the reference (uw-mad-dash/LV-XAttn) it stands in for.
+ *
+ * Layouts (all tensors dense, row-major in the listed order):
+ *   q, dO, o        [B, Hq,  Sq,  D]   element type = shape.dtype
+ *   k, v, dk, dv    [B, Hkv, Skv, D]   element type = shape.dtype (dk/dv accumulators: fp32)
+ *   lse, delta      [B*Hq, Sq]         fp32, natural-log log-sum-exp / rowsum(O*dO)
+ *   Hq must be a multiple of Hkv; query head h reads KV head h / (Hq/Hkv).  D must be 128.
+ */
+#ifndef LVX_H_
+#define LVX_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LVX_ABI_VERSION 1
+
+enum lvx_dtype { LVX_BF16 = 0, LVX_FP16 = 1, LVX_FP32 = 2 /* computed with TF32 tensor-core operands */ };
+
+enum lvx_error {
+  LVX_OK = 0,
+  LVX_ERR_NULL = -1,        /* a required pointer is NULL                       */
+  LVX_ERR_SHAPE = -2,       /* unsupported or inconsistent shape                */
+  LVX_ERR_DTYPE = -3,       /* unsupported dtype                                */
+  LVX_ERR_ALIGN = -4,       /* a pointer is not 16-byte aligned                 */
+  LVX_ERR_WORKSPACE = -5,   /* workspace too small                              */
+  LVX_ERR_ARCH = -6,        /* current device is not compute capability 10.x    */
+  LVX_ERR_DRIVER = -7,      /* a driver entry point could not be resolved       */
+  LVX_ERR_LIMIT = -8        /* size beyond a documented fixed limit             */
+};
+
+typedef struct lvx_shape {
+  int32_t B;       /* batch                                  */
+  int32_t Hq;      /* query heads                            */
+  int32_t Hkv;     /* key/value heads (divides Hq)           */
+  int32_t Sq;      /* query rows of the block being processed */
+  int32_t Skv;     /* key/value rows resident on this GPU    */
+  int32_t D;       /* head dimension (128)                   */
+  int32_t dtype;   /* enum lvx_dtype                         */
+  int32_t reserved;
+} lvx_shape;
+
+/* Library / ABI version (LVX_ABI_VERSION). No reference counterpart (the reference is pure Python). */
+int lvx_version(void);
+
+/* Text of the last error on the calling thread. Replaces the reference's Python asserts
+ * (lv_xattn/attn.py:305-309, lv_xattn/flash_attn_kernels.py:913-917) as the error channel. */
+const char* lvx_last_error(void);
+
+/* Device status word of the last kernels launched by this library on the current device
+ * (0 = fine; otherwise the code of the bounded wait that ran out). Reads the word, clears it and
+ * synchronises the stream it is given; while the word is non-zero every kernel of the library
+ * returns at once without computing. The reference has no equivalent: its waits are unbounded
+ * (lv_xattn/async_communication.py:301-305). */
+int lvx_device_status(void* stream, int* status_out);
+
+/* Bytes of scratch the forward / backward block kernels need for this shape.
+ * Stands in for the per-step torch allocations in lv_xattn/attn.py:382-385 and
+ * lv_xattn/flash_attn_kernels.py:920-921. */
+int lvx_query_workspace(const lvx_shape* s, size_t* fwd_bytes, size_t* bwd_bytes);
+
+/* One flash-attention forward block: the Q block [B,Hq,Sq,D] against the resident K/V shard.
+ * Writes split-KV partial results (unnormalised O, running max, running sum) into `workspace`;
+ * lvx_fwd_combine_merge turns them into (O, lse).
+ * kv_valid_len (nullable, int32 [B], device): number of leading K/V rows of this shard that are
+ * valid for each batch entry (key padding); rows beyond it contribute nothing.
+ * Replaces the Triton _fwd_kernel and its launch, lv_xattn/attn.py:140-268 and :390-400, and the
+ * K/V head expansion lv_xattn/attn.py:271-277 (GQA is handled inside the kernel). */
+int lvx_fwd_block(const lvx_shape* s, const void* q, const void* k, const void* v,
+                  const int32_t* kv_valid_len, float sm_scale, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* Reduce the split-KV partials of lvx_fwd_block and merge the result into the travelling
+ * accumulator:  (o_in, lse_in) (+) partials -> (o_out, lse_out).
+ * o_in / lse_in may be NULL, meaning the empty accumulator (O = 0, lse = -inf).
+ * o_in, o_out are fp32 [B,Hq,Sq,D] when out_is_final == 0 (the travelling form); when
+ * out_is_final != 0, o_out is written in shape.dtype (the tensor handed back to the caller).
+ * The merge is log-sum-exp stable and yields (0, -inf) when both sides are empty.
+ * Replaces _rescale_kernel, lv_xattn/attn.py:37-110 and :405-419. */
+int lvx_fwd_combine_merge(const lvx_shape* s, const void* workspace, const float* o_in, const float* lse_in,
+                          void* o_out, float* lse_out, int out_is_final, void* stream);
+
+/* delta[b*Hq+h, i] = sum_d O[b,h,i,d] * dO[b,h,i,d]  (fp32).
+ * Replaces _bwd_preprocess_do_o_dot, lv_xattn/flash_attn_kernels.py:287-329. */
+int lvx_bwd_prep(const lvx_shape* s, const void* o, const void* d_o, float* delta, void* stream);
+
+/* One flash-attention backward block: recomputes P from (q, k, lse), then
+ *   dq_acc[B,Hq,Sq,D]   (fp32) += dS K            (reduce-add; the caller zeroes it)
+ *   dk_acc[B,Hkv,Skv,D] (fp32) (+)= dS^T Q        (summed over the query heads of the KV group)
+ *   dv_acc[B,Hkv,Skv,D] (fp32) (+)= P^T dO
+ * accumulate_dkdv == 0 overwrites dk_acc/dv_acc, != 0 adds to them.
+ * Replaces _flash_attn_backward / _bwd_kernel, lv_xattn/flash_attn_kernels.py:904-1020 and
+ * :364-819, and the per-step accumulation lv_xattn/attn.py:523-527. */
+int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const float* lse, const float* delta,
+                  const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
+                  float* dk_acc, float* dv_acc, int accumulate_dkdv, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
+/* out[i] = (dtype) (a[i] + b[i]) over n fp32 elements; b may be NULL; out_dtype is an lvx_dtype
+ * (LVX_FP32 keeps fp32). Used for: travelling dQ += local dQ, and the final down-cast of
+ * dQ/dK/dV. Replaces lv_xattn/attn.py:527 and lv_xattn/flash_attn_kernels.py:1020. */
+int lvx_add_cast(const float* a, const float* b, void* out, int out_dtype, size_t n, void* stream);
+
+/* Self-test of the tensor-core building blocks (TMA tile load, shared-memory and TMEM operand
+ * descriptors, TMEM load/store): runs one 128 x N x K product in the operand arrangement `mode`
+ * and writes D (fp32 [128,N]) to `d_out`. a/b are device buffers in the arrangement the mode
+ * documents (see csrc/selftest.cu). No reference counterpart. */
+int lvx_selftest_mma(int mode, const void* a, const void* b, float* d_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LVX_H_ */

@@ -1,0 +1,134 @@
+"""Tensor-level wrappers over the C ABI (include/lvx.h). All compute happens in liblvx.so; torch only owns
+the device memory and the stream. Inputs must be CUDA tensors; anything else raises."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _lib.LvxError("lv_xattn_b200 runs on CUDA tensors only; there is no CPU path")
+
+
+def _contig(t):
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """One cached scratch buffer per device, grown on demand (module-owned; see release_workspaces)."""
+    key = (device.type, device.index)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+
+
+def shape_of(q, k) -> _lib.LvxShape:
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Skv, Dk = k.shape
+    if Bk != B or Dk != D:
+        raise ValueError(f"q {tuple(q.shape)} and k {tuple(k.shape)} disagree on batch or head dimension")
+    if Hq % Hkv:
+        raise ValueError(f"{Hq} query heads are not a multiple of {Hkv} KV heads")
+    return _lib.make_shape(B, Hq, Hkv, Sq, Skv, D, q.dtype)
+
+
+def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, final=True):
+    """(O, lse) of the Q block against the local K/V shard, merged into the travelling (o_in, lse_in).
+
+    final=True  -> O in q.dtype (the caller's result); final=False -> fp32 travelling form.
+    lse is fp32 [B*Hq, Sq]."""
+    _require_cuda(q, k, v, kv_valid_len, o_in, lse_in)
+    lib = _lib.load()
+    q, k, v = _contig(q), _contig(k), _contig(v)
+    if v.shape != k.shape or v.dtype != q.dtype or k.dtype != q.dtype:
+        raise ValueError("k and v must have the same shape, and q/k/v the same dtype")
+    shp = shape_of(q, k)
+    fwd_bytes, _ = _lib.query_workspace(shp)
+    ws = _workspace(q.device, fwd_bytes)
+    B, Hq, Sq, D = q.shape
+    if kv_valid_len is not None:
+        if kv_valid_len.dtype != torch.int32 or kv_valid_len.numel() != B:
+            raise ValueError("kv_valid_len must be an int32 tensor with one entry per batch element")
+        kv_valid_len = _contig(kv_valid_len)
+    st = _lib.stream_ptr()
+    _lib.check(lib.lvx_fwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len),
+                                 ctypes.c_float(sm_scale), _lib.ptr(ws), ws.numel(), st), "lvx_fwd_block")
+    o_out = torch.empty(B, Hq, Sq, D, dtype=q.dtype if final else torch.float32, device=q.device)
+    lse_out = torch.empty(B * Hq, Sq, dtype=torch.float32, device=q.device)
+    if o_in is not None:
+        if o_in.dtype != torch.float32 or lse_in is None or lse_in.dtype != torch.float32:
+            raise ValueError("the travelling accumulator (o_in, lse_in) must be fp32")
+        o_in, lse_in = _contig(o_in), _contig(lse_in)
+    _lib.check(lib.lvx_fwd_combine_merge(ctypes.byref(shp), _lib.ptr(ws), _lib.ptr(o_in), _lib.ptr(lse_in),
+                                         _lib.ptr(o_out), _lib.ptr(lse_out), 1 if final else 0, st),
+               "lvx_fwd_combine_merge")
+    return o_out, lse_out
+
+
+def bwd_prep(o, do):
+    """delta [B*Hq, Sq] fp32 = rowsum(O * dO)."""
+    _require_cuda(o, do)
+    lib = _lib.load()
+    o, do = _contig(o), _contig(do)
+    B, Hq, Sq, D = o.shape
+    shp = _lib.make_shape(B, Hq, Hq, Sq, 0, D, o.dtype)
+    delta = torch.empty(B * Hq, Sq, dtype=torch.float32, device=o.device)
+    _lib.check(lib.lvx_bwd_prep(ctypes.byref(shp), _lib.ptr(o), _lib.ptr(do), _lib.ptr(delta), _lib.stream_ptr()),
+               "lvx_bwd_prep")
+    return delta
+
+
+def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None):
+    """dq_acc += dS K ; dk_acc, dv_acc (+)= dS^T Q, P^T dO  (all fp32 accumulators, updated in place)."""
+    _require_cuda(q, do, lse, delta, k, v, dq_acc, dk_acc, dv_acc, kv_valid_len)
+    lib = _lib.load()
+    q, do, k, v = _contig(q), _contig(do), _contig(k), _contig(v)
+    shp = shape_of(q, k)
+    for t, name in ((lse, "lse"), (delta, "delta"), (dq_acc, "dq_acc"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous fp32 tensor")
+    if dq_acc.numel() != q.numel() or dk_acc.numel() != k.numel() or dv_acc.numel() != v.numel():
+        raise ValueError("accumulator sizes do not match q / k / v")
+    if kv_valid_len is not None:
+        kv_valid_len = _contig(kv_valid_len)
+    _lib.check(lib.lvx_bwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
+                                 _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale),
+                                 _lib.ptr(dq_acc), _lib.ptr(dk_acc), _lib.ptr(dv_acc), 1 if accumulate_dkdv else 0,
+                                 None, 0, _lib.stream_ptr()), "lvx_bwd_block")
+
+
+def add_cast(a, b, out_dtype):
+    """cast(a + b) for fp32 a (and optional fp32 b of the same shape)."""
+    _require_cuda(a, b)
+    lib = _lib.load()
+    a = _contig(a)
+    if a.dtype != torch.float32 or (b is not None and (b.dtype != torch.float32 or b.shape != a.shape)):
+        raise ValueError("add_cast takes fp32 tensors of equal shape")
+    if b is not None:
+        b = _contig(b)
+    out = torch.empty(a.shape, dtype=out_dtype, device=a.device)
+    _lib.check(lib.lvx_add_cast(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.dtype_code(out_dtype), a.numel(),
+                                _lib.stream_ptr()), "lvx_add_cast")
+    return out
+
+
+def selftest_mma(mode: int, a, b, n_cols: int):
+    _require_cuda(a, b)
+    lib = _lib.load()
+    d = torch.empty(128, n_cols, dtype=torch.float32, device=a.device)
+    _lib.check(lib.lvx_selftest_mma(mode, _lib.ptr(a), _lib.ptr(b), _lib.ptr(d), _lib.stream_ptr()),
+               "lvx_selftest_mma")
+    return d

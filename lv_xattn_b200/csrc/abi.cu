@@ -54,7 +54,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 int make_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
-                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
+                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1, bool swizzle_atom_32b) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(LVX_ERR_DRIVER, "cuTensorMapEncodeTiled could not be resolved");
   CUtensorMapDataType dt = dtype == LVX_BF16   ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -68,7 +68,8 @@ int make_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t dim0, u
   cuuint32_t box[3] = {box0, box1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle_atom_32b ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(LVX_ERR_SHAPE, "cuTensorMapEncodeTiled failed with CUresult %d (dims %llu,%llu,%llu box %u,%u)",
                 int(r), (unsigned long long)dim0, (unsigned long long)dim1, (unsigned long long)dim2, box0, box1);

@@ -16,7 +16,8 @@ int cuda_fail(cudaError_t e, const char* what);
 // Encodes a 3-D tiled tensor map with 128-byte swizzle. dims/strides are given innermost first;
 // stride[0] is implied by the element size. box2 is always 1. Returns an ABI status code.
 int make_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t dim0, uint64_t dim1, uint64_t dim2,
-                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1);
+                 uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
+                 bool swizzle_atom_32b = false);
 
 inline int elt_size(int dtype) { return dtype == LVX_FP32 ? 4 : 2; }
 

@@ -136,14 +136,16 @@ selftest_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // K-major: step 32 bytes inside the 128-byte row, next swizzle atom after 4 steps.
         // MN-major: step kstep rows of 128 bytes.
         uint64_t bdesc, adesc = 0;
+        // 32-bit MN-major operands use the 32-byte-unit swizzle: K rows in groups of 4 (512 bytes)
+        const uint32_t mn_sbo = c.elt == 4 ? 512 : 1024, mn_type = c.elt == 4 ? 1 : 2;
         if (c.b_major == 0)
           bdesc = umma_smem_desc(b_base + (kk >> 2) * b_rows * 128 + (kk & 3) * 32, 16, 1024);
         else
-          bdesc = umma_smem_desc(b_base + kk * kstep * 128, b_rows * 128, 1024);
+          bdesc = umma_smem_desc(b_base + kk * kstep * 128, b_rows * 128, mn_sbo, mn_type);
         if (c.a_src == 0)
           adesc = umma_smem_desc(a_base + (kk >> 2) * a_rows * 128 + (kk & 3) * 32, 16, 1024);
         else if (c.a_src == 1)
-          adesc = umma_smem_desc(a_base + kk * kstep * 128, a_rows * 128, 1024);
+          adesc = umma_smem_desc(a_base + kk * kstep * 128, a_rows * 128, mn_sbo, mn_type);
         const uint32_t acc = kk > 0;
         if (c.elt == 2) {
           if (c.a_src == 2) umma_ts_f16(tmem_d, tmem_a + kk * 8, bdesc, idesc, acc);
@@ -185,24 +187,20 @@ int launch_selftest(int mode, const void* a, const void* b, float* d_out, int* s
   int rc;
   const int b_rows = c.b_major == 0 ? c.N : c.K, b_cols = c.b_major == 0 ? c.K : c.N;
   rc = make_tmap_3d(&tmB, dtype, b, b_cols, b_rows, 1, uint64_t(b_cols) * c.elt, uint64_t(b_cols) * b_rows * c.elt,
-                    epr, b_rows);
+                    epr, b_rows, c.elt == 4 && c.b_major == 1);
   if (rc) return rc;
   if (c.a_src != 2) {
     const int a_rows = c.a_src == 0 ? 128 : c.K, a_cols = c.a_src == 0 ? c.K : 128;
     rc = make_tmap_3d(&tmA, dtype, a, a_cols, a_rows, 1, uint64_t(a_cols) * c.elt,
-                      uint64_t(a_cols) * a_rows * c.elt, epr, a_rows);
+                      uint64_t(a_cols) * a_rows * c.elt, epr, a_rows, c.elt == 4 && c.a_src == 1);
     if (rc) return rc;
   } else {
     tmA = tmB;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(selftest)");
-    attr_set = true;
-  }
+  cudaError_t e = cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(selftest)");
   selftest_kernel<<<1, 128, ST_SMEM, st>>>(tmA, tmB, a, d_out, mode, status);
-  cudaError_t e = cudaGetLastError();
+  e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "selftest launch");
   return LVX_OK;
 }

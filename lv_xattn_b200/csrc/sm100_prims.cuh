@@ -135,13 +135,18 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 // MN-major operand (rows = K index, 128-byte row holds 128/elt_size consecutive M or N):
 //     stride byte offset = distance between 8-row (K) groups (1024),
 //     leading byte offset = distance between successive 128-byte-wide column blocks along M/N.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+//
+// layout_type 2 = 128-byte swizzle in 16-byte units (all 16-bit operands, 32-bit K-major operands);
+// layout_type 1 = 128-byte swizzle in 32-byte units (CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B), the form
+// 32-bit MN-major operands need: K rows come in groups of 4 (stride byte offset = 512).
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 

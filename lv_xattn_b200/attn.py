@@ -1,0 +1,327 @@
+"""LV-XAttn step loop: sequence-parallel cross-attention forward and backward.
+
+Same entry points, argument order and return conventions as the reference's lv_xattn/attn.py
+(`_attn_forward` :297-435, `_attn_backward` :437-545), plus the two autograd wrappers the reference's
+drivers build around them (test.py:38-77 "save q,k,v"; test_llama3.py:180-245 "recompute q,k,v").
+
+Sharding (reference test.py:164-178): rank r holds rows [r*Sq/W, (r+1)*Sq/W) of Q/dO/O and rows
+[r*Skv/W, (r+1)*Skv/W) of K/V. K/V never move. At step t a rank works on the Q block born on rank r-t:
+  forward   partials = flash block(Q_blk, local K/V)            (tensor-core kernel, independent of the ring)
+            acc_out  = merge(acc_in, partials)                  (one HBM-bound kernel; acc_in arrives from r-1)
+            acc_out -> rank r+1; after W hops the finished (O, lse) is back home
+  backward  dQ_delta, dK+=, dV+= = flash bwd block(Q_blk, dO_blk, lse_blk, delta_blk, local K/V)
+            dQ_out = dQ_in + dQ_delta -> rank r+1; after W hops dQ is home
+Differences from the reference that are deliberate: the travelling accumulators are fp32 (reference: fp16,
+:448,:527), the empty accumulator is (0, -inf) instead of lse = 0 (:319), the result is taken from the slot
+that actually holds it for every W (reference returns slot 0, wrong for odd W, :435), delta is computed once
+at home and travels instead of O (:926-942 recomputes it on every rank), K/V are used at their own head
+count (no expansion, :392-393), and key padding is a per-batch valid length instead of a dense bias.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .async_communication import (
+    _exchange,
+    get_sequence_parallel_rank,
+    get_sequence_parallel_size,
+    get_slabs,
+    reset_global_memory_buffer,
+    send_recv_bwd_comp_reqs,
+    send_recv_bwd_rescale_reqs,
+    send_recv_fwd_Lo,
+    send_recv_fwd_q,
+    wait_async_handles,
+)
+
+_SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
+
+
+def _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args):
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+        raise ValueError("q, k, v must be [batch, heads, seq, head_dim]")
+    Dq, Dk, Dv = q.shape[-1], k.shape[-1], v.shape[-1]
+    if not (Dq == Dk == Dv):
+        raise ValueError(f"head dimensions differ: {Dq}, {Dk}, {Dv}")
+    if Dq != 128:
+        raise ValueError(f"head dimension {Dq} unsupported (128 only)")
+    if k.shape[-2] != v.shape[-2] or k.shape[1] != v.shape[1]:
+        raise ValueError("k and v must agree on heads and sequence length")
+    if q.shape[1] % k.shape[1]:
+        raise ValueError(f"{q.shape[1]} query heads are not a multiple of {k.shape[1]} KV heads")
+    if q.dtype not in _SUPPORTED or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("q, k, v must share one dtype out of bfloat16, float16, float32")
+    if bias_func is None:
+        if len(local_bias_args) or len(remote_bias_args):
+            raise ValueError("bias arguments given without a bias_func")
+    else:
+        raise NotImplementedError(
+            "dense additive bias_func is not supported; key padding is expressed with kv_valid_len")
+    if causal:
+        raise NotImplementedError(
+            "causal=True is not supported: cross-attention has no causal order, and the reference applies "
+            "the mask with rank-local indices at every step (lv_xattn/attn.py:229,237)")
+
+
+def _local_valid(kv_valid_len, skv_local: int, device):
+    """Global key-padding lengths [B] -> this rank's clamp min(max(valid - rank*Skv_l, 0), Skv_l)."""
+    if kv_valid_len is None:
+        return None
+    t = torch.as_tensor(kv_valid_len, device=device).to(torch.int64)
+    t = (t - get_sequence_parallel_rank() * skv_local).clamp_(0, skv_local)
+    return t.to(torch.int32).contiguous()
+
+
+def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> torch.Tensor:
+    n = 1
+    for s in shape:
+        n *= s
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    return buf[offset:offset + nbytes].view(dtype).view(*shape)
+
+
+def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bias_args=[], remote_bias_args=[],
+                  no_overlap=False, kv_valid_len=None):
+    """Returns (q, k, v, o, L): o like q, L fp32 [B*Hq, Sq_local] natural-log lse (reference :297-435).
+
+    comm_mode == "nocomm" runs the W-step schedule without any transfer (timing ablation, as in the
+    reference :294-296); the result is then the attention of the local Q block over the local K/V only.
+    kv_valid_len: optional global number of valid K/V rows per batch entry (key padding)."""
+    _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args)
+    W = get_sequence_parallel_size()
+    B, Hq, Sq, D = q.shape
+    dev, dt = q.device, q.dtype
+    es = q.element_size()
+    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    kvl = _local_valid(kv_valid_len, k.shape[2], dev)
+    o = torch.empty(B, Hq, Sq, D, dtype=dt, device=dev)
+    L = torch.empty(B * Hq, Sq, dtype=torch.float32, device=dev)
+
+    if W == 1 or comm_mode == "nocomm":
+        for _ in range(W):
+            part = ops.fwd_partials(qc, kc, vc, sm_scale, kvl)
+            ops.fwd_combine(part, None, None, o, L, True)
+        return q, k, v, o, L
+
+    n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
+    acc_bytes = n_o * 4 + n_l * 4
+    q_bufs = get_slabs("fwd_q", n_o * es, dev, 2)
+    send_bufs = get_slabs("fwd_acc_send", acc_bytes, dev, 2)
+    recv_bufs = get_slabs("fwd_acc_recv", acc_bytes, dev, 2)
+
+    def acc_views(buf, final):
+        odt = dt if final else torch.float32
+        o_v = _carve(buf, 0, (B, Hq, Sq, D), odt)
+        l_v = _carve(buf, n_o * (es if final else 4), (B * Hq, Sq), torch.float32)
+        return o_v, l_v
+
+    q_cur = qc
+    q_reqs, acc_reqs = [], []
+    for t in range(W):
+        last = t == W - 1
+        wait_async_handles(q_reqs)          # the block this step works on has arrived
+        q_reqs = []
+        if not last:
+            q_next = _carve(q_bufs[t % 2], 0, (B, Hq, Sq, D), dt)
+            q_reqs = send_recv_fwd_q(q_cur, q_next, [], [], comm_mode)
+            if no_overlap:
+                wait_async_handles(q_reqs)
+                q_reqs = []
+        part = ops.fwd_partials(q_cur, kc, vc, sm_scale, kvl)
+        wait_async_handles(acc_reqs)        # travelling accumulator of this block (and last step's send)
+        o_in = l_in = None
+        if t > 0:
+            o_in, l_in = acc_views(recv_bufs[(t - 1) % 2], False)
+        o_out, l_out = acc_views(send_bufs[t % 2], last)
+        ops.fwd_combine(part, o_in, l_in, o_out, l_out, last)
+        if last:
+            # the finished block goes home; this rank's own finished block arrives from rank-1
+            acc_reqs = _exchange_final(o_out, l_out, o, L, comm_mode)
+        else:
+            sv = send_bufs[t % 2][:acc_bytes]
+            rv = recv_bufs[t % 2][:acc_bytes]
+            acc_reqs = send_recv_fwd_Lo(sv, rv, comm_mode)
+        if no_overlap:
+            wait_async_handles(acc_reqs)
+            acc_reqs = []
+        if not last:
+            q_cur = q_next
+    wait_async_handles(acc_reqs)
+    return q, k, v, o, L
+
+
+def _exchange_final(o_send, l_send, o_recv, l_recv, comm_mode):
+    return _exchange([o_send, l_send], [o_recv, l_recv], comm_mode)
+
+
+def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engine, bias_func=None,
+                   local_bias_args=[], remote_bias_args=[], no_overlap=False, kv_valid_len=None):
+    """Returns (dq, dk, dv): dq like q, dk/dv like k/v (summed over the query heads of each KV group)
+    (reference :437-545). `backward_engine` is accepted and ignored, as in the reference."""
+    _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args)
+    W = get_sequence_parallel_size()
+    B, Hq, Sq, D = q.shape
+    Hkv, Skv = k.shape[1], k.shape[2]
+    dev, dt = q.device, q.dtype
+    es = q.element_size()
+    qc, kc, vc, oc, doc = (x.contiguous() for x in (q, k, v, o, do))
+    if L.dtype != torch.float32 or L.numel() != B * Hq * Sq:
+        raise ValueError("L must be the fp32 [B*Hq, Sq] log-sum-exp returned by _attn_forward")
+    Lc = L.contiguous().view(B * Hq, Sq)
+    kvl = _local_valid(kv_valid_len, Skv, dev)
+
+    n_q, n_r, n_kv = B * Hq * Sq * D, B * Hq * Sq, B * Hkv * Skv * D
+    delta = ops.bwd_prep(oc, doc)                       # once, at home; travels instead of O
+    acc = get_slabs("bwd_dkdv", 2 * n_kv * 4, dev, 1)[0]
+    dk_acc = _carve(acc, 0, (B, Hkv, Skv, D), torch.float32)
+    dv_acc = _carve(acc, n_kv * 4, (B, Hkv, Skv, D), torch.float32)
+    dq = torch.empty(B, Hq, Sq, D, dtype=dt, device=dev)
+
+    if W == 1 or comm_mode == "nocomm":
+        dq_acc = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
+        for t in range(W):
+            dq_acc.zero_()
+            ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk_acc, dv_acc, False, kvl)
+        ops.add_cast(dq_acc, None, dt, out=dq)
+    else:
+        slab_bytes = 2 * n_q * es + 2 * n_r * 4
+        in_bufs = get_slabs("bwd_in", slab_bytes, dev, 3)
+        dq_delta = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
+        send_bufs = get_slabs("bwd_dq_send", n_q * 4, dev, 2)
+        recv_bufs = get_slabs("bwd_dq_recv", n_q * 4, dev, 2)
+
+        def slab_views(buf):
+            return (_carve(buf, 0, (B, Hq, Sq, D), dt), _carve(buf, n_q * es, (B, Hq, Sq, D), dt),
+                    _carve(buf, 2 * n_q * es, (B * Hq, Sq), torch.float32),
+                    _carve(buf, 2 * n_q * es + n_r * 4, (B * Hq, Sq), torch.float32))
+
+        # home slab: [Q | dO | lse | delta]
+        cur = in_bufs[2]
+        cq, cdo, cl, cd = slab_views(cur)
+        cq.copy_(qc)
+        cdo.copy_(doc)
+        cl.copy_(Lc)
+        cd.copy_(delta)
+        comp_reqs, dq_reqs = [], []
+        for t in range(W):
+            last = t == W - 1
+            wait_async_handles(comp_reqs)
+            comp_reqs = []
+            cq, cdo, cl, cd = slab_views(cur)
+            if not last:
+                nxt = in_bufs[t % 2]
+                comp_reqs = send_recv_bwd_comp_reqs(cur[:slab_bytes], nxt[:slab_bytes], [], [], comm_mode)
+                if no_overlap:
+                    wait_async_handles(comp_reqs)
+                    comp_reqs = []
+            # step 0 accumulates straight into the buffer that is sent on; later steps into a scratch
+            # delta that is added to the accumulator received from rank-1
+            send_v = _carve(send_bufs[t % 2], 0, (B, Hq, Sq, D), torch.float32)
+            target = send_v if t == 0 else dq_delta
+            target.zero_()
+            ops.bwd_block(cq, cdo, cl, cd, kc, vc, sm_scale, target, dk_acc, dv_acc, t > 0, kvl)
+            wait_async_handles(dq_reqs)
+            if t > 0:
+                recv_v = _carve(recv_bufs[(t - 1) % 2], 0, (B, Hq, Sq, D), torch.float32)
+                if last:
+                    fin = _carve(send_bufs[t % 2], 0, (B, Hq, Sq, D), dt)
+                    ops.add_cast(recv_v, dq_delta, dt, out=fin)
+                else:
+                    ops.add_cast(recv_v, dq_delta, torch.float32, out=send_v)
+            if last:
+                fin = _carve(send_bufs[t % 2], 0, (B, Hq, Sq, D), dt)
+                dq_reqs = send_recv_bwd_rescale_reqs(fin, dq, comm_mode)
+            else:
+                dq_reqs = send_recv_bwd_rescale_reqs(send_bufs[t % 2][:n_q * 4], recv_bufs[t % 2][:n_q * 4],
+                                                     comm_mode)
+            if no_overlap:
+                wait_async_handles(dq_reqs)
+                dq_reqs = []
+            if not last:
+                cur = nxt
+        wait_async_handles(dq_reqs)
+
+    dk = ops.add_cast(dk_acc, None, dt)
+    dv = ops.add_cast(dv_acc, None, dt)
+    return dq, dk, dv
+
+
+# --------------------------------------------------------------------------------------------------
+# autograd wrappers
+# --------------------------------------------------------------------------------------------------
+class LVXAttnFunc(torch.autograd.Function):
+    """attention(q, k, v, causal, sm_scale, bias_func=None, local_bias_args=[], remote_bias_args=[]) -> o.
+    Saves q, k, v, o, L for backward; same call shape as the class built in reference test.py:38-77."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, bias_func=None, local_bias_args=[], remote_bias_args=[],
+                kv_valid_len=None):
+        q, k, v, o, L = _attn_forward(q, k, v, causal, sm_scale, None, bias_func=bias_func,
+                                      local_bias_args=local_bias_args, remote_bias_args=remote_bias_args,
+                                      kv_valid_len=kv_valid_len)
+        ctx.save_for_backward(q, k, v, o, L)
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+        ctx.kv_valid_len = kv_valid_len
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, L = ctx.saved_tensors
+        dq, dk, dv = _attn_backward(do, q, k, v, o, L, ctx.causal, ctx.sm_scale, None, "flash",
+                                    kv_valid_len=ctx.kv_valid_len)
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+class LVXAttnRecomputeFunc(torch.autograd.Function):
+    """attention(x, run_function, is_causal, *params) -> o, where run_function(x, states) -> (q, k, v) is the
+    projection of the layer and `states` are the visual features held in a module global
+    (see hf_patch.set_global_cross_attention_states). Only (x, o, L) are saved: K/V are recomputed in
+    backward, which keeps the per-layer activation memory independent of the visual sequence length
+    (reference test_llama3.py:180-245). Unlike the reference (:243 returns None for every input), backward
+    re-runs the projection under autograd and propagates dq, dk, dv into x and into `params` (the tensors
+    run_function closes over, passed so that autograd sees them)."""
+
+    @staticmethod
+    def forward(ctx, x, run_function, is_causal, states_getter, kv_valid_len, *params):
+        with torch.no_grad():
+            q, k, v = run_function(x, states_getter())
+        sm_scale = q.shape[-1] ** -0.5
+        _, _, _, o, L = _attn_forward(q, k, v, is_causal, sm_scale, None, kv_valid_len=kv_valid_len)
+        ctx.save_for_backward(x, o, L, *params)
+        ctx.run_function = run_function
+        ctx.states_getter = states_getter
+        ctx.is_causal = is_causal
+        ctx.sm_scale = sm_scale
+        ctx.kv_valid_len = kv_valid_len
+        del q, k, v
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        x, o, L, *params = ctx.saved_tensors
+        with torch.enable_grad():
+            x_ = x.detach().requires_grad_(x.requires_grad)
+            q, k, v = ctx.run_function(x_, ctx.states_getter())
+        dq, dk, dv = _attn_backward(do, q.detach(), k.detach(), v.detach(), o, L, ctx.is_causal, ctx.sm_scale,
+                                    None, "flash", kv_valid_len=ctx.kv_valid_len)
+        inputs = [t for t in ([x_] + list(params)) if t.requires_grad]
+        grads = torch.autograd.grad((q, k, v), inputs, (dq, dk, dv), allow_unused=True) if inputs else ()
+        it = iter(grads)
+        gx = next(it) if x_.requires_grad else None
+        gparams = [next(it) if p.requires_grad else None for p in params]
+        return (gx, None, None, None, None, *gparams)
+
+
+def create_attention_class(attention_mode="lv_xattn"):
+    """Same factory as reference test.py:38: returns the autograd class for `attention_mode`."""
+    if attention_mode != "lv_xattn":
+        raise NotImplementedError(f"attention_mode {attention_mode!r}: only 'lv_xattn' is built")
+    return LVXAttnFunc
+
+
+attention = LVXAttnFunc.apply
+
+__all__ = ["_attn_forward", "_attn_backward", "LVXAttnFunc", "LVXAttnRecomputeFunc", "create_attention_class",
+           "attention", "reset_global_memory_buffer"]

@@ -10,6 +10,48 @@ from . import _lib
 
 _workspaces: dict = {}
 
+# Launch accounting for benchmarks: number of kernels of this library launched since the last reset, and
+# (when profiling is on) CUDA event pairs around the two tensor-core kernels, recorded on the launch stream.
+launch_count = 0
+_profile = None   # None, or {"fwd": [(start, end), ...], "bwd": [...]}
+
+
+def set_profiling(on: bool) -> None:
+    global _profile
+    _profile = {"fwd": [], "bwd": []} if on else None
+
+
+def take_profile():
+    """Returns {"fwd": [ms, ...], "bwd": [ms, ...]} for the launches since set_profiling(True); the caller
+    must have synchronised the device."""
+    global _profile
+    out = {k: [a.elapsed_time(b) for a, b in v] for k, v in (_profile or {}).items()}
+    if _profile is not None:
+        _profile = {"fwd": [], "bwd": []}
+    return out
+
+
+class _Timed:
+    def __init__(self, kind):
+        self.kind = kind
+
+    def __enter__(self):
+        if _profile is not None:
+            self.a = torch.cuda.Event(enable_timing=True)
+            self.b = torch.cuda.Event(enable_timing=True)
+            self.a.record()
+
+    def __exit__(self, *exc):
+        if _profile is not None:
+            self.b.record()
+            _profile[self.kind].append((self.a, self.b))
+        return False
+
+
+def _count(n=1):
+    global launch_count
+    launch_count += n
+
 
 def _require_cuda(*ts):
     for t in ts:
@@ -45,12 +87,18 @@ def shape_of(q, k) -> _lib.LvxShape:
     return _lib.make_shape(B, Hq, Hkv, Sq, Skv, D, q.dtype)
 
 
-def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, final=True):
-    """(O, lse) of the Q block against the local K/V shard, merged into the travelling (o_in, lse_in).
+class FwdPartials:
+    """Handle on the split-KV partials of one forward block (they live in the module's workspace until
+    the next forward block on the same device overwrites them)."""
+    __slots__ = ("shape", "ws", "dims", "dtype", "device")
 
-    final=True  -> O in q.dtype (the caller's result); final=False -> fp32 travelling form.
-    lse is fp32 [B*Hq, Sq]."""
-    _require_cuda(q, k, v, kv_valid_len, o_in, lse_in)
+    def __init__(self, shape, ws, dims, dtype, device):
+        self.shape, self.ws, self.dims, self.dtype, self.device = shape, ws, dims, dtype, device
+
+
+def fwd_partials(q, k, v, sm_scale, kv_valid_len=None) -> FwdPartials:
+    """Launches the forward block: Q block x local K/V shard -> split-KV partials in the workspace."""
+    _require_cuda(q, k, v, kv_valid_len)
     lib = _lib.load()
     q, k, v = _contig(q), _contig(k), _contig(v)
     if v.shape != k.shape or v.dtype != q.dtype or k.dtype != q.dtype:
@@ -58,23 +106,48 @@ def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, fina
     shp = shape_of(q, k)
     fwd_bytes, _ = _lib.query_workspace(shp)
     ws = _workspace(q.device, fwd_bytes)
-    B, Hq, Sq, D = q.shape
+    B = q.shape[0]
     if kv_valid_len is not None:
         if kv_valid_len.dtype != torch.int32 or kv_valid_len.numel() != B:
             raise ValueError("kv_valid_len must be an int32 tensor with one entry per batch element")
         kv_valid_len = _contig(kv_valid_len)
-    st = _lib.stream_ptr()
-    _lib.check(lib.lvx_fwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len),
-                                 ctypes.c_float(sm_scale), _lib.ptr(ws), ws.numel(), st), "lvx_fwd_block")
+    with _Timed("fwd"):
+        _lib.check(lib.lvx_fwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+                                     _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale), _lib.ptr(ws), ws.numel(),
+                                     _lib.stream_ptr()), "lvx_fwd_block")
+    _count()
+    return FwdPartials(shp, ws, tuple(q.shape), q.dtype, q.device)
+
+
+def fwd_combine(part: FwdPartials, o_in, lse_in, o_out, lse_out, final: bool) -> None:
+    """partials (+) travelling (o_in, lse_in) -> (o_out, lse_out). o_in/lse_in None = empty accumulator.
+    final=True writes O in the input dtype, otherwise fp32 (the travelling form)."""
+    _require_cuda(o_in, lse_in, o_out, lse_out)
+    lib = _lib.load()
+    want = part.dtype if final else torch.float32
+    if o_out.dtype != want or lse_out.dtype != torch.float32 or not o_out.is_contiguous() or not lse_out.is_contiguous():
+        raise ValueError(f"o_out must be contiguous {want}, lse_out contiguous fp32")
+    if (o_in is None) != (lse_in is None):
+        raise ValueError("o_in and lse_in go together")
+    if o_in is not None and (o_in.dtype != torch.float32 or lse_in.dtype != torch.float32
+                             or not o_in.is_contiguous() or not lse_in.is_contiguous()):
+        raise ValueError("the travelling accumulator (o_in, lse_in) must be contiguous fp32")
+    _lib.check(lib.lvx_fwd_combine_merge(ctypes.byref(part.shape), _lib.ptr(part.ws), _lib.ptr(o_in),
+                                         _lib.ptr(lse_in), _lib.ptr(o_out), _lib.ptr(lse_out), 1 if final else 0,
+                                         _lib.stream_ptr()), "lvx_fwd_combine_merge")
+    _count()
+
+
+def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, final=True):
+    """(O, lse) of the Q block against the local K/V shard, merged into the travelling (o_in, lse_in).
+
+    final=True  -> O in q.dtype (the caller's result); final=False -> fp32 travelling form.
+    lse is fp32 [B*Hq, Sq]."""
+    part = fwd_partials(q, k, v, sm_scale, kv_valid_len)
+    B, Hq, Sq, D = q.shape
     o_out = torch.empty(B, Hq, Sq, D, dtype=q.dtype if final else torch.float32, device=q.device)
     lse_out = torch.empty(B * Hq, Sq, dtype=torch.float32, device=q.device)
-    if o_in is not None:
-        if o_in.dtype != torch.float32 or lse_in is None or lse_in.dtype != torch.float32:
-            raise ValueError("the travelling accumulator (o_in, lse_in) must be fp32")
-        o_in, lse_in = _contig(o_in), _contig(lse_in)
-    _lib.check(lib.lvx_fwd_combine_merge(ctypes.byref(shp), _lib.ptr(ws), _lib.ptr(o_in), _lib.ptr(lse_in),
-                                         _lib.ptr(o_out), _lib.ptr(lse_out), 1 if final else 0, st),
-               "lvx_fwd_combine_merge")
+    fwd_combine(part, o_in, lse_in, o_out, lse_out, final)
     return o_out, lse_out
 
 
@@ -88,6 +161,7 @@ def bwd_prep(o, do):
     delta = torch.empty(B * Hq, Sq, dtype=torch.float32, device=o.device)
     _lib.check(lib.lvx_bwd_prep(ctypes.byref(shp), _lib.ptr(o), _lib.ptr(do), _lib.ptr(delta), _lib.stream_ptr()),
                "lvx_bwd_prep")
+    _count()
     return delta
 
 
@@ -104,14 +178,16 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
         raise ValueError("accumulator sizes do not match q / k / v")
     if kv_valid_len is not None:
         kv_valid_len = _contig(kv_valid_len)
-    _lib.check(lib.lvx_bwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
-                                 _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale),
-                                 _lib.ptr(dq_acc), _lib.ptr(dk_acc), _lib.ptr(dv_acc), 1 if accumulate_dkdv else 0,
-                                 None, 0, _lib.stream_ptr()), "lvx_bwd_block")
+    with _Timed("bwd"):
+        _lib.check(lib.lvx_bwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
+                                     _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale),
+                                     _lib.ptr(dq_acc), _lib.ptr(dk_acc), _lib.ptr(dv_acc),
+                                     1 if accumulate_dkdv else 0, None, 0, _lib.stream_ptr()), "lvx_bwd_block")
+    _count()
 
 
-def add_cast(a, b, out_dtype):
-    """cast(a + b) for fp32 a (and optional fp32 b of the same shape)."""
+def add_cast(a, b, out_dtype, out=None):
+    """cast(a + b) for fp32 a (and optional fp32 b of the same shape); written into `out` when given."""
     _require_cuda(a, b)
     lib = _lib.load()
     a = _contig(a)
@@ -119,9 +195,13 @@ def add_cast(a, b, out_dtype):
         raise ValueError("add_cast takes fp32 tensors of equal shape")
     if b is not None:
         b = _contig(b)
-    out = torch.empty(a.shape, dtype=out_dtype, device=a.device)
+    if out is None:
+        out = torch.empty(a.shape, dtype=out_dtype, device=a.device)
+    elif out.dtype != out_dtype or out.numel() != a.numel() or not out.is_contiguous() or not out.is_cuda:
+        raise ValueError("out must be a contiguous CUDA tensor of the requested dtype and size")
     _lib.check(lib.lvx_add_cast(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.dtype_code(out_dtype), a.numel(),
                                 _lib.stream_ptr()), "lvx_add_cast")
+    _count()
     return out
 
 

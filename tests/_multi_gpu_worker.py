@@ -1,0 +1,43 @@
+"""One NCCL rank of tests/test_gpu_multi.py (launched by torch.distributed.run)."""
+import math
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import torch  # noqa: E402
+
+import lv_xattn_b200 as lvx  # noqa: E402
+from lv_xattn_b200 import _lib  # noqa: E402
+from oracle import attention_oracle as orc  # noqa: E402
+
+rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(local)
+dev = torch.device("cuda", local)
+lvx.initialize_distributed("nccl")
+scale = 1.0 / math.sqrt(128.0)
+cases = [
+    (1, 8, 2, 128 * world, 1024 * world, torch.bfloat16, None),
+    (2, 4, 2, 64 * world, 512 * world, torch.bfloat16, [512 * world, 512 * world * 3 // 4]),
+]
+for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
+    q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 31, dtype)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, scale, valid)
+    ql, dol, kl, vl = (orc.shard(t, rank, world).to(dev) for t in (q, do, k, v))
+    for rep in range(2):
+        _, _, _, o, L = lvx._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid)
+        dq, dk, dv = lvx._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    Sl = Sq // world
+    lse_l = orc.shard(lse_ref.unsqueeze(-1), rank, world).squeeze(-1)
+    errs = {
+        "o": (o.float().cpu() - orc.shard(o_ref, rank, world)).abs().max().item(),
+        "lse": (L.cpu().view(B, Hq, Sl) - lse_l).abs().max().item(),
+        "dq": (dq.float().cpu() - orc.shard(dq_ref, rank, world)).abs().max().item(),
+        "dk": (dk.float().cpu() - orc.shard(dk_ref, rank, world)).abs().max().item(),
+        "dv": (dv.float().cpu() - orc.shard(dv_ref, rank, world)).abs().max().item(),
+    }
+    assert errs["lse"] <= 1e-3 and all(errs[n] <= 2e-2 for n in ("o", "dq", "dk", "dv")), (rank, errs)
+print(f"RANK_OK {rank}", flush=True)
+torch.distributed.destroy_process_group()

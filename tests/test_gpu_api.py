@@ -1,0 +1,77 @@
+"""The reference-facing Python entry points on one GPU: _attn_forward / _attn_backward, the save-QKV autograd
+wrapper and the recompute-QKV wrapper, against the CPU oracle."""
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / math.sqrt(128.0)
+
+
+def test_forward_backward_entry_points(cuda_device):
+    import lv_xattn_b200 as lvx
+    B, Hq, Hkv, Sq, Skv = 2, 8, 2, 128, 1024
+    q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 21, torch.bfloat16)
+    o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, SCALE, [1024, 700])
+    d = cuda_device
+    qd, kd, vd, dod = (t.to(d) for t in (q, k, v, do))
+    q2, k2, v2, o, L = lvx._attn_forward(qd, kd, vd, False, SCALE, None, kv_valid_len=[1024, 700])
+    assert q2 is qd and k2 is kd and v2 is vd
+    assert o.shape == qd.shape and o.dtype == qd.dtype and L.shape == (B * Hq, Sq) and L.dtype == torch.float32
+    dq, dk, dv = lvx._attn_backward(dod, qd, kd, vd, o, L, False, SCALE, None, "flash", kv_valid_len=[1024, 700])
+    assert dq.shape == qd.shape and dk.shape == kd.shape and dv.shape == vd.shape and dk.dtype == kd.dtype
+    assert (o.float().cpu() - o_ref).abs().max() <= 2e-2
+    assert (L.cpu().view(B, Hq, Sq) - lse_ref).abs().max() <= 1e-3
+    for g, r in ((dq, dq_ref), (dk, dk_ref), (dv, dv_ref)):
+        assert (g.float().cpu() - r).abs().max() <= 2e-2
+
+
+def test_autograd_wrapper(cuda_device):
+    import lv_xattn_b200 as lvx
+    B, Hq, Hkv, Sq, Skv = 1, 4, 4, 256, 512
+    q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 22, torch.float16)
+    _, _, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, SCALE)
+    d = cuda_device
+    qd, kd, vd = (t.to(d).requires_grad_(True) for t in (q, k, v))
+    attention = lvx.create_attention_class("lv_xattn").apply
+    o = attention(qd, kd, vd, False, SCALE)
+    o.backward(do.to(d))
+    for g, r in ((qd.grad, dq_ref), (kd.grad, dk_ref), (vd.grad, dv_ref)):
+        assert (g.float().cpu() - r).abs().max() <= 2e-2
+
+
+def test_recompute_wrapper_propagates_gradients(cuda_device):
+    """K/V are recomputed in backward and the gradients reach x and the projection weights (the reference's
+    wrapper drops them, test_llama3.py:243)."""
+    import lv_xattn_b200 as lvx
+    d = cuda_device
+    torch.manual_seed(3)
+    B, Sq, Skv, H, hid = 1, 64, 512, 2, 256
+    x = (torch.randn(B, Sq, hid, device=d) * 0.5).bfloat16().requires_grad_(True)
+    states = (torch.randn(B, Skv, hid, device=d) * 0.5).bfloat16()
+    wq, wk, wv = ((torch.randn(hid, H * 128, device=d) * 0.05).bfloat16().requires_grad_(True) for _ in range(3))
+
+    def project(xx, st):
+        q = (xx @ wq).view(B, Sq, H, 128).transpose(1, 2)
+        k = (st @ wk).view(B, Skv, H, 128).transpose(1, 2)
+        v = (st @ wv).view(B, Skv, H, 128).transpose(1, 2)
+        return q, k, v
+
+    o = lvx.LVXAttnRecomputeFunc.apply(x, project, False, lambda: states, None, wq, wk, wv)
+    go = torch.randn_like(o)
+    o.backward(go)
+    got = [t.grad.float().clone() for t in (x, wq, wk, wv)]
+    for t in (x, wq, wk, wv):
+        t.grad = None
+    # same layer with plain fp32 attention math through autograd
+    q, k, v = project(x, states)
+    p = torch.softmax((q.float() @ k.float().transpose(2, 3)) * (128 ** -0.5), dim=-1)
+    o_ref = (p @ v.float())
+    o_ref.backward(go.float())
+    assert (o.float() - o_ref).abs().max() <= 2e-2
+    for g, t in zip(got, (x, wq, wk, wv)):
+        ref = t.grad.float()
+        assert (g - ref).abs().max() <= 3e-2 * max(1.0, ref.abs().max().item()), (g - ref).abs().max()

@@ -22,6 +22,7 @@
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
 #include <math.h>
+#include <stdlib.h>
 
 namespace lvx {
 
@@ -72,6 +73,7 @@ struct BwdParams {
   float* dk_acc;       // [slab][skv][128]
   float* dv_acc;
   int accumulate;
+  int debug;           // development switches (LVX_BWD_DEBUG); 0 in normal use
   int* status;
 };
 
@@ -284,7 +286,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (h * 32 + i < ncols)
+            if (h * 32 + i < ncols && !(p.debug & 1))
               atomicAdd(dq_base + size_t(q0 + h * 32 + i) * 128, __uint_as_float(v[h][i]) * p.scale);
       }
       // ------------------------------- dV epilogue -------------------------------
@@ -458,6 +460,10 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   p.dv_acc = dv_acc;
   p.accumulate = accumulate_dkdv;
   p.status = status;
+  {
+    const char* dbg = getenv("LVX_BWD_DEBUG");
+    p.debug = dbg ? atoi(dbg) : 0;
+  }
 
   dim3 grid((s.Skv + 127) / 128, s.B * s.Hkv, 1);
   cudaError_t e;

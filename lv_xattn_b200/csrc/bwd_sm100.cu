@@ -12,17 +12,20 @@
 // written once; dQ^T tiles are reduce-added (red.global.add.f32) into the fp32 dQ accumulator. The
 // softmax scale is applied once on the way out (dK, dQ).
 //
-// CTA anatomy (320 threads)
-//   warps 0-3  P^T/dS^T producers: thread = K/V row (TMEM lane); epilogue of dK
-//   warps 4-7  dQ reducers: thread = head-dim index (TMEM lane of dQ^T); epilogue of dV
-//   warp  8    TMA producer: K,V once; Q,dO tiles through a 3-stage ring
-//   warp  9    tcgen05.mma issuer; owns the TMEM allocation
+// CTA anatomy (448 threads)
+//   warps 0-7   P^T/dS^T producers: thread = K/V row (TMEM lane = 32*(warp%4)+lane); warps 0-3 take query
+//               columns 0-31 of the tile, warps 4-7 columns 32-63 (two warps per scheduler hide each other's
+//               latencies); epilogue: warps 0-3 write dK, warps 4-7 write dV
+//   warps 8-11  dQ reducers: thread = head-dim index (TMEM lane of dQ^T)
+//   warp  12    TMA producer: K,V once; Q,dO tiles through a 3-stage ring
+//   warp  13    tcgen05.mma issuer; owns the TMEM allocation
 //   TMEM columns: dK [0,128) dV [128,256) S^T x2 [256,384) dP^T [384,448) dQ^T [448,512);
 //   P^T and dS^T (16-bit, 32 columns each) overwrite the S^T buffer they came from.
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
 #include <math.h>
 #include <stdlib.h>
+#include <stdio.h>
 
 namespace lvx {
 
@@ -39,7 +42,7 @@ constexpr int BWD_OFF_DS = BWD_OFF_Q + BWD_NSQ * 2 * BWD_Q_BYTES;
 constexpr int BWD_OFF_STAT = BWD_OFF_DS + 2 * BWD_DS_BYTES;         // lse2[3][64], delta[3][64]
 constexpr int BWD_OFF_BAR = BWD_OFF_STAT + 6 * 64 * 4;
 constexpr int BWD_SMEM = BWD_OFF_BAR + 256 + 1024;
-constexpr int BWD_THREADS = 320;
+constexpr int BWD_THREADS = 448;
 
 constexpr uint32_t TM_DK = 0, TM_DV = 128, TM_S = 256, TM_DP = 384, TM_DQ = 448;
 
@@ -76,6 +79,14 @@ struct BwdParams {
   int debug;           // development switches (LVX_BWD_DEBUG); 0 in normal use
   int* status;
 };
+
+// Development aid (LVX_BWD_DEBUG bit 128): cycle stamps of CTA (0,0), tiles 8..15, 16 slots per tile and role.
+__device__ long long g_bwd_ts[3 * 8 * 16];
+#define BWD_TS(role, slot)                                                                         \
+  do {                                                                                             \
+    if ((p.debug & 128) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && j >= 8 && j < 16)    \
+      g_bwd_ts[((role) * 8 + (j - 8)) * 16 + (slot)] = clock64();                                  \
+  } while (0)
 
 #define BWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x200 | ((role) << 5) | (bar))
 
@@ -133,20 +144,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars[BB_S_FULL + b], 1);
-      mbar_init(&bars[BB_PDS_FULL + b], 128);
+      mbar_init(&bars[BB_PDS_FULL + b], 8);    // one arrival per producer warp
       mbar_init(&bars[BB_DS_FREE + b], 1);
     }
     mbar_init(&bars[BB_DP_FULL], 1);
-    mbar_init(&bars[BB_DP_FREE], 128);
+    mbar_init(&bars[BB_DP_FREE], 8);
     mbar_init(&bars[BB_DQ_FULL], 1);
-    mbar_init(&bars[BB_DQ_FREE], 128);
+    mbar_init(&bars[BB_DQ_FREE], 4);
     mbar_init(&bars[BB_ACC_DONE], 1);
     mbar_init(&bars[BB_DRAIN], 1);
-    for (int b = 0; b < 3; ++b) mbar_init(&bars[BB_STAT_FULL + b], 128);
+    for (int b = 0; b < 3; ++b) mbar_init(&bars[BB_STAT_FULL + b], 4);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == 13) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -156,14 +167,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   const uint32_t tmem_base = *tmem_slot;
 
   if (!poisoned && tile_live) {
-    if (warp < 4) {
+    if (warp < 8) {
       // =========================== P^T / dS^T producers ===========================
-      const int r = warp * 32 + lane;                       // K/V row inside the tile
+      const int half = warp >> 2;                           // which 32 query columns of the tile
+      const int r = (warp & 3) * 32 + lane;                 // K/V row inside the tile
       const bool row_valid = (kv0 + r) < valid;
-      const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+      const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
       const float c = p.scale_log2;
       const size_t stat_base = size_t(slab) * p.rows;
-      // statistics of the next query tile, fetched one tile ahead: threads 0-63 lse, 64-127 delta
+      // statistics of the next query tile, fetched one tile ahead by threads 0-63 (lse) and 64-127 (delta)
       auto fetch_stat = [&](int j) -> float {
         const int col = tid & 63;
         const int qrow = j * 64 + col;
@@ -175,63 +187,79 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           }
           return v;
         }
-        return qrow < p.rows ? p.delta[stat_base + qrow] : 0.f;
+        return (tid < 128 && qrow < p.rows) ? p.delta[stat_base + qrow] : 0.f;
       };
       // Three buffers: a thread may run one tile ahead of the slowest thread of the group (the
       // dP^T hand-over keeps them within one tile of each other), and it writes tile j+1 while in tile j.
       auto put_stat = [&](int j, float v) {
+        if (tid >= 128) return;
         const int b = j % 3;
         if (tid < 64) s_lse[b * 64 + tid] = v;
         else s_delta[b * 64 + (tid - 64)] = v;
-        mbar_arrive(&bars[BB_STAT_FULL + b]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[BB_STAT_FULL + b]);
       };
       put_stat(0, fetch_stat(0));
+      // The statistics are fetched two tiles ahead (global-memory latency is longer than one tile's work)
+      // and published one tile ahead.
+      float stat_next = nq > 1 ? fetch_stat(1) : 0.f;
       bool alive = true;
       for (int j = 0; j < nq; ++j) {
         const int b = j & 1;
+        if (warp == 0) BWD_TS(0, 0);
         const uint32_t tS = tmem_base + TM_S + b * 64 + lane_sel;
         const uint32_t tDP = tmem_base + TM_DP + lane_sel;
-        float next_stat = 0.f;
-        if (j + 1 < nq) next_stat = fetch_stat(j + 1);
+        float stat_after = 0.f;
+        if (j + 2 < nq) stat_after = fetch_stat(j + 2);
         if (!mbar_wait(&bars[BB_S_FULL + b], (j >> 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL)) ||
             !mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL))) {
           alive = false;
           break;
         }
         tc_fence_after();
-        uint32_t s[2][32], dp[2][32];
-        tmem_ld32(tS, s[0]);
-        tmem_ld32(tS + 32, s[1]);
-        tmem_ld32(tDP, dp[0]);
-        tmem_ld32(tDP + 32, dp[1]);
+        if (warp == 0) BWD_TS(0, 1);
+        uint32_t s[32], dp[32];
+        tmem_ld32(tS + half * 32, s);
+        tmem_ld32(tDP + half * 32, dp);
         tc_wait_ld();
+        if (warp == 0) BWD_TS(0, 2);
         tc_fence_before();
-        mbar_arrive(&bars[BB_DP_FREE]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[BB_DP_FREE]);
         if (!mbar_wait(&bars[BB_STAT_FULL + j % 3], (j / 3) & 1, abort_flag, p.status, BWD_CODE(0, BB_STAT_FULL))) {
           alive = false;
           break;
         }
-        const float* sl = s_lse + (j % 3) * 64;
-        const float* sd = s_delta + (j % 3) * 64;
-        uint32_t pk[32], dsk[32];
+        if (warp == 0) BWD_TS(0, 3);
+        const float4* sl = reinterpret_cast<const float4*>(s_lse + (j % 3) * 64 + half * 32);
+        const float4* sd = reinterpret_cast<const float4*>(s_delta + (j % 3) * 64 + half * 32);
+        uint32_t pk[16], dsk[16];
+        if (p.debug & 2) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+          for (int i = 0; i < 16; ++i) { pk[i] = s[i]; dsk[i] = dp[i]; }
+        } else
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int c0 = h * 32 + 2 * i;
-            const float2 l2 = *reinterpret_cast<const float2*>(sl + c0);
-            const float2 dl = *reinterpret_cast<const float2*>(sd + c0);
-            float p0 = ex2f(fmaf(__uint_as_float(s[h][2 * i]), c, -l2.x));
-            float p1 = ex2f(fmaf(__uint_as_float(s[h][2 * i + 1]), c, -l2.y));
-            if (!row_valid) { p0 = 0.f; p1 = 0.f; }
-            const float d0 = p0 * (__uint_as_float(dp[h][2 * i]) - dl.x);
-            const float d1 = p1 * (__uint_as_float(dp[h][2 * i + 1]) - dl.y);
-            pk[h * 16 + i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-            dsk[h * 16 + i] = IS_BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
-          }
+        for (int i = 0; i < 8; ++i) {
+          const float4 l2 = sl[i];
+          const float4 dl = sd[i];
+          float p0 = ex2f(fmaf(__uint_as_float(s[4 * i]), c, -l2.x));
+          float p1 = ex2f(fmaf(__uint_as_float(s[4 * i + 1]), c, -l2.y));
+          float p2 = ex2f(fmaf(__uint_as_float(s[4 * i + 2]), c, -l2.z));
+          float p3 = ex2f(fmaf(__uint_as_float(s[4 * i + 3]), c, -l2.w));
+          if (!row_valid) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
+          const float d0 = p0 * (__uint_as_float(dp[4 * i]) - dl.x);
+          const float d1 = p1 * (__uint_as_float(dp[4 * i + 1]) - dl.y);
+          const float d2 = p2 * (__uint_as_float(dp[4 * i + 2]) - dl.z);
+          const float d3 = p3 * (__uint_as_float(dp[4 * i + 3]) - dl.w);
+          pk[2 * i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+          pk[2 * i + 1] = IS_BF16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
+          dsk[2 * i] = IS_BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
+          dsk[2 * i + 1] = IS_BF16 ? pack_bf16x2(d2, d3) : pack_f16x2(d2, d3);
         }
-        tmem_st32(tS, pk);
-        tmem_st32(tS + 32, dsk);
+        if (warp == 0) BWD_TS(0, 4);
+        tmem_st16(tS + half * 16, pk);
+        tmem_st16(tS + 32 + half * 16, dsk);
+        if (warp == 0) BWD_TS(0, 5);
         // dS^T row -> shared memory, 128-byte swizzled (16-byte chunk index xor row mod 8)
         if (j >= 2 &&
             !mbar_wait(&bars[BB_DS_FREE + b], ((j >> 1) - 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_DS_FREE))) {
@@ -239,32 +267,41 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           tc_wait_st();
           break;
         }
-        {
+        if (!(p.debug & 32)) {
           uint8_t* rowp = smem + BWD_OFF_DS + b * BWD_DS_BYTES + r * 128;
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
+          for (int ch = 0; ch < 4; ++ch) {
             uint4 v = make_uint4(dsk[4 * ch], dsk[4 * ch + 1], dsk[4 * ch + 2], dsk[4 * ch + 3]);
-            *reinterpret_cast<uint4*>(rowp + ((ch ^ (r & 7)) << 4)) = v;
+            *reinterpret_cast<uint4*>(rowp + (((half * 4 + ch) ^ (r & 7)) << 4)) = v;
           }
         }
-        if (j + 1 < nq) put_stat(j + 1, next_stat);
+        if (warp == 0) BWD_TS(0, 6);
+        if (j + 1 < nq) put_stat(j + 1, stat_next);
+        stat_next = stat_after;
+        if (warp == 0) BWD_TS(0, 7);
         tc_wait_st();
+        if (warp == 0) BWD_TS(0, 8);
         tc_fence_before();
-        fence_async_smem();
-        mbar_arrive(&bars[BB_PDS_FULL + b]);
+        if (!(p.debug & 32)) fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[BB_PDS_FULL + b]);
+        if (warp == 0) BWD_TS(0, 9);
       }
-      // ------------------------------- dK epilogue -------------------------------
+      // ------------------------------- dK / dV epilogue -------------------------------
       if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], 0, abort_flag, p.status, BWD_CODE(0, BB_ACC_DONE));
       tc_fence_after();
       if (alive) {
         const bool ok_row = (kv0 + r) < p.skv;
-        float* dst = p.dk_acc + (size_t(slab) * p.skv + kv0 + r) * 128;
-        store_acc_row(tmem_base + TM_DK + lane_sel, dst, ok_row, p.accumulate != 0, p.scale);
+        const size_t off = (size_t(slab) * p.skv + kv0 + r) * 128;
+        if (half == 0)
+          store_acc_row(tmem_base + TM_DK + lane_sel, p.dk_acc + off, ok_row, p.accumulate != 0, p.scale);
+        else
+          store_acc_row(tmem_base + TM_DV + lane_sel, p.dv_acc + off, ok_row, p.accumulate != 0, 1.f);
       }
-    } else if (warp < 8) {
+    } else if (warp < 12) {
       // =========================== dQ reducers ===========================
-      const int d = (warp - 4) * 32 + lane;                  // head-dim index = TMEM lane of dQ^T
-      const uint32_t lane_sel = static_cast<uint32_t>((warp - 4) * 32) << 16;
+      const int d = (warp - 8) * 32 + lane;                  // head-dim index = TMEM lane of dQ^T
+      const uint32_t lane_sel = static_cast<uint32_t>((warp - 8) * 32) << 16;
       const uint32_t tDQ = tmem_base + TM_DQ + lane_sel;
       float* dq_base = p.dq_acc + size_t(slab) * p.rows * 128 + d;
       bool alive = true;
@@ -273,13 +310,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           alive = false;
           break;
         }
+        if (warp == 8) BWD_TS(1, 0);
         tc_fence_after();
         uint32_t v[2][32];
         tmem_ld32(tDQ, v[0]);
         tmem_ld32(tDQ + 32, v[1]);
         tc_wait_ld();
         tc_fence_before();
-        mbar_arrive(&bars[BB_DQ_FREE]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);
+        if (warp == 8) BWD_TS(1, 1);
         const int q0 = j * 64;
         const int ncols = min(64, p.rows - q0);
 #pragma unroll
@@ -289,16 +329,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (h * 32 + i < ncols && !(p.debug & 1))
               atomicAdd(dq_base + size_t(q0 + h * 32 + i) * 128, __uint_as_float(v[h][i]) * p.scale);
       }
-      // ------------------------------- dV epilogue -------------------------------
-      if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], 0, abort_flag, p.status, BWD_CODE(1, BB_ACC_DONE));
-      tc_fence_after();
-      if (alive) {
-        const int r = d;
-        const bool ok_row = (kv0 + r) < p.skv;
-        float* dst = p.dv_acc + (size_t(slab) * p.skv + kv0 + r) * 128;
-        store_acc_row(tmem_base + TM_DV + lane_sel, dst, ok_row, p.accumulate != 0, 1.f);
-      }
-    } else if (warp == 8) {
+      (void)alive;
+    } else if (warp == 12) {
       // =========================== TMA producer ===========================
       if (lane == 0) {
         tma_prefetch_desc(&tmQ);
@@ -316,10 +348,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const uint32_t ph = (j / BWD_NSQ) & 1;
           if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY))) break;
           uint8_t* dstq = smem + BWD_OFF_Q + s * 2 * BWD_Q_BYTES;
-          mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_Q_BYTES);
-          for (int h = 0; h < 2; ++h) {
-            tma_load_3d(dstq + h * BWD_Q_HALF, &tmQ, &bars[BB_Q_FULL + s], h * 64, j * 64, slab);
-            tma_load_3d(dstq + BWD_Q_BYTES + h * BWD_Q_HALF, &tmDO, &bars[BB_Q_FULL + s], h * 64, j * 64, slab);
+          if (p.debug & 64) {
+            mbar_arrive(&bars[BB_Q_FULL + s]);
+          } else {
+            mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_Q_BYTES);
+            for (int h = 0; h < 2; ++h) {
+              tma_load_3d(dstq + h * BWD_Q_HALF, &tmQ, &bars[BB_Q_FULL + s], h * 64, j * 64, slab);
+              tma_load_3d(dstq + BWD_Q_BYTES + h * BWD_Q_HALF, &tmDO, &bars[BB_Q_FULL + s], h * 64, j * 64, slab);
+            }
           }
           issued = j + 1;
         }
@@ -342,26 +378,31 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint32_t sK = smem_u32(smem + BWD_OFF_K), sV = smem_u32(smem + BWD_OFF_V);
         const uint32_t sQ0 = smem_u32(smem + BWD_OFF_Q), sDS0 = smem_u32(smem + BWD_OFF_DS);
 
+        constexpr uint32_t HI = umma_desc_hi(1024);
         // D[128 kv, 64 q] = A[128 kv, 128 d] * B[64 q, 128 d]^T, both K-major
         auto issue_st = [&](uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem) {
+          const uint32_t a_lo = umma_desc_lo(a_smem, 16), b_lo = umma_desc_lo(b_smem, 16);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss_f16(d_tmem, umma_smem_desc(a_smem + (kk >> 2) * BWD_KV_HALF + (kk & 3) * 32, 16, 1024),
-                        umma_smem_desc(b_smem + (kk >> 2) * BWD_Q_HALF + (kk & 3) * 32, 16, 1024), IDESC_S, kk > 0);
+            umma_ss_f16(d_tmem, umma_desc_join(a_lo + (((kk >> 2) * BWD_KV_HALF + (kk & 3) * 32) >> 4), HI),
+                        umma_desc_join(b_lo + (((kk >> 2) * BWD_Q_HALF + (kk & 3) * 32) >> 4), HI), IDESC_S, kk > 0);
         };
         // D[128 kv, 128 d] += A_tmem[128 kv, 64 q] * B[64 q, 128 d]  (B MN-major: rows are q)
         auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem, bool first) {
+          const uint32_t b_lo = umma_desc_lo(b_smem, BWD_Q_HALF);
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
-            umma_ts_f16(d_tmem, a_tmem + kk * 8, umma_smem_desc(b_smem + kk * 2048, BWD_Q_HALF, 1024), IDESC_ACC,
+            umma_ts_f16(d_tmem, a_tmem + kk * 8, umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_ACC,
                         (!first) || kk > 0);
         };
         // D[128 d, 64 q] = K^T[128 d, 128 kv] * dS^T[128 kv, 64 q]  (both MN-major: rows are kv)
+        const uint32_t kT_lo = umma_desc_lo(sK, BWD_KV_HALF);
         auto issue_dq = [&](uint32_t ds_smem) {
+          const uint32_t b_lo = umma_desc_lo(ds_smem, BWD_DS_BYTES);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_ss_f16(tmem_base + TM_DQ, umma_smem_desc(sK + kk * 2048, BWD_KV_HALF, 1024),
-                        umma_smem_desc(ds_smem + kk * 2048, BWD_DS_BYTES, 1024), IDESC_DQ, kk > 0);
+            umma_ss_f16(tmem_base + TM_DQ, umma_desc_join(kT_lo + ((kk * 2048) >> 4), HI),
+                        umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_DQ, kk > 0);
         };
 
         bool ok = mbar_wait(&bars[BB_KV_FULL], 0, abort_flag, p.status, BWD_CODE(3, BB_KV_FULL));
@@ -375,6 +416,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         for (int j = 0; ok && j < nq; ++j) {
           const int b = j & 1, s = j % BWD_NSQ;
+          BWD_TS(2, 0);
           const uint32_t sQ = sQ0 + s * 2 * BWD_Q_BYTES, sDO = sQ + BWD_Q_BYTES;
           if (j + 1 < nq) {
             const int s1 = (j + 1) % BWD_NSQ, b1 = (j + 1) & 1;
@@ -382,28 +424,38 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             ok = mbar_wait(&bars[BB_Q_FULL + s1], ((j + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL));
             if (!ok) break;
             tc_fence_after();
-            issue_st(tmem_base + TM_S + b1 * 64, sK, sQ1);
+            BWD_TS(2, 1);
+            if (!(p.debug & 8)) issue_st(tmem_base + TM_S + b1 * 64, sK, sQ1);
             tc_commit(&bars[BB_S_FULL + b1]);
+            BWD_TS(2, 2);
             ok = mbar_wait(&bars[BB_DP_FREE], j & 1, abort_flag, p.status, BWD_CODE(3, BB_DP_FREE));
             if (!ok) break;
             tc_fence_after();
-            issue_st(tmem_base + TM_DP, sV, sQ1 + BWD_Q_BYTES);
+            BWD_TS(2, 3);
+            if (!(p.debug & 8)) issue_st(tmem_base + TM_DP, sV, sQ1 + BWD_Q_BYTES);
             tc_commit(&bars[BB_DP_FULL]);
+            BWD_TS(2, 4);
           }
           ok = mbar_wait(&bars[BB_PDS_FULL + b], (j >> 1) & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL));
           if (!ok) break;
           tc_fence_after();
-          issue_acc(tmem_base + TM_DV, tmem_base + TM_S + b * 64, sDO, j == 0);
-          issue_acc(tmem_base + TM_DK, tmem_base + TM_S + b * 64 + 32, sQ, j == 0);
+          BWD_TS(2, 5);
+          if (!(p.debug & 16)) {
+            issue_acc(tmem_base + TM_DV, tmem_base + TM_S + b * 64, sDO, j == 0);
+            issue_acc(tmem_base + TM_DK, tmem_base + TM_S + b * 64 + 32, sQ, j == 0);
+          }
           tc_commit(&bars[BB_Q_EMPTY + s]);
+          BWD_TS(2, 6);
           if (j > 0) {
             ok = mbar_wait(&bars[BB_DQ_FREE], (j - 1) & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE));
             if (!ok) break;
             tc_fence_after();
           }
-          issue_dq(sDS0 + b * BWD_DS_BYTES);
+          BWD_TS(2, 7);
+          if (!(p.debug & 4)) issue_dq(sDS0 + b * BWD_DS_BYTES);
           tc_commit(&bars[BB_DQ_FULL]);
           tc_commit(&bars[BB_DS_FREE + b]);
+          BWD_TS(2, 8);
         }
         if (ok) {
           tc_commit(&bars[BB_ACC_DONE]);
@@ -426,7 +478,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) tmem_dealloc(tmem_base, 512);
+  if (warp == 13) tmem_dealloc(tmem_base, 512);
 }
 
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
@@ -478,6 +530,18 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "bwd_kernel launch");
+  if (p.debug & 128) {
+    static long long ts[3 * 8 * 16];
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(ts, g_bwd_ts, sizeof(ts));
+    const char* names[3] = {"softmax", "reducer", "mma"};
+    for (int r = 0; r < 3; ++r)
+      for (int j = 0; j < 8; ++j) {
+        fprintf(stderr, "%s tile %d:", names[r], j + 8);
+        for (int k = 0; k < 10; ++k) fprintf(stderr, " %lld", ts[(r * 8 + j) * 16 + k] ? ts[(r * 8 + j) * 16 + k] - ts[0] : -1);
+        fprintf(stderr, "\n");
+      }
+  }
   return LVX_OK;
 }
 

@@ -95,7 +95,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars[FB_S_FULL + i], 1);
-      mbar_init(&bars[FB_P_FULL + i], 128);
+      mbar_init(&bars[FB_P_FULL + i], 4);      // one arrival per softmax warp
       mbar_init(&bars[FB_O_DONE + i], 1);
     }
     mbar_init(&bars[FB_DRAIN], 1);
@@ -191,7 +191,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         l += sum0 + sum1;
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars[FB_P_FULL + wg]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[FB_P_FULL + wg]);
       }
       // ------------------------------- epilogue -------------------------------
       const int row = mb * 256 + wg * 128 + row_in_tile;
@@ -262,21 +263,23 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint32_t sK = smem_u32(smem + FWD_OFF_K);
         const uint32_t sV = smem_u32(smem + FWD_OFF_V);
 
+        constexpr uint32_t HI = umma_desc_hi(1024);
         auto issue_qk = [&](int i, int stage) {
-          const uint32_t a0 = sQ + i * FWD_TILE_BYTES, b0 = sK + stage * FWD_TILE_BYTES;
+          const uint32_t a_lo = umma_desc_lo(sQ + i * FWD_TILE_BYTES, 16);
+          const uint32_t b_lo = umma_desc_lo(sK + stage * FWD_TILE_BYTES, 16);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t off = (kk >> 2) * FWD_HALF_BYTES + (kk & 3) * 32;
-            umma_ss_f16(tmem_base + i * 128, umma_smem_desc(a0 + off, 16, 1024), umma_smem_desc(b0 + off, 16, 1024),
-                        IDESC_QK, kk > 0);
+            const uint32_t off = ((kk >> 2) * FWD_HALF_BYTES + (kk & 3) * 32) >> 4;
+            umma_ss_f16(tmem_base + i * 128, umma_desc_join(a_lo + off, HI), umma_desc_join(b_lo + off, HI), IDESC_QK,
+                        kk > 0);
           }
         };
         auto issue_pv = [&](int i, int stage, bool first) {
-          const uint32_t b0 = sV + stage * FWD_TILE_BYTES;
+          const uint32_t b_lo = umma_desc_lo(sV + stage * FWD_TILE_BYTES, FWD_HALF_BYTES);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             umma_ts_f16(tmem_base + 256 + i * 128, tmem_base + i * 128 + kk * 8,
-                        umma_smem_desc(b0 + kk * 2048, FWD_HALF_BYTES, 1024), IDESC_PV, (!first) || kk > 0);
+                        umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_PV, (!first) || kk > 0);
         };
 
         bool ok = mbar_wait(&bars[FB_Q_FULL], 0, abort_flag, p.status, FWD_CODE(3, FB_Q_FULL));

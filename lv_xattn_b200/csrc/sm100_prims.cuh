@@ -150,6 +150,22 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The two 32-bit halves of the descriptor. Along a K loop only the start address changes, so the issuing
+// thread keeps `hi` and a base `lo` in registers and adds a compile-time constant (byte offset >> 4) per
+// step -- one integer add per operand instead of rebuilding the 64-bit value (the issuing thread is a
+// single lane; every scalar instruction it spends per MMA is tensor-pipe idle time).
+__device__ __forceinline__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes, uint32_t layout_type = 2) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout_type << 29);
+}
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t umma_desc_join(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 enum : uint32_t { UMMA_F16 = 0, UMMA_BF16 = 1, UMMA_TF32 = 2 };
 enum : uint32_t { UMMA_K_MAJOR = 0, UMMA_MN_MAJOR = 1 };
 

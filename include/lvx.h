@@ -115,6 +115,22 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
  * dQ/dK/dV. Replaces lv_xattn/attn.py:527 and lv_xattn/flash_attn_kernels.py:1020. */
 int lvx_add_cast(const float* a, const float* b, void* out, int out_dtype, size_t n, void* stream);
 
+/* Forward block + combine in one call that allocates nothing: (O, lse) of the Q block against the
+ * K/V shard, O written in shape.dtype, lse fp32 [B*Hq, Sq]. This entry point has no counterpart in
+ * the reference; it exists for callers that must not touch the device allocator when they call
+ * (no cudaMalloc / cudaFree / framework allocator on a path that has a fixed memory budget or must
+ * not synchronise the device). The split-KV partials go to a 32 MiB scratch area built into the
+ * library image (held by every GPU that loads the library until the process exits) instead of a
+ * caller workspace. The number of K/V splits is lowered until the partials fit; a shape whose
+ * unsplit partials exceed the area (more than about 64,500 rows B*Hq*Sq) is refused with
+ * LVX_ERR_LIMIT. The first call on a device looks up the area's device address; make that first
+ * call outside any stream capture. All calls share the area, which keeps the previous call's
+ * contents (the kernel overwrites every entry it later reads, so nothing needs clearing); two calls
+ * whose kernels overlap on the GPU -- different streams or devices' streams on one GPU -- race on it. */
+int lvx_fwd_block_static(const lvx_shape* s, const void* q, const void* k, const void* v,
+                         const int32_t* kv_valid_len, float sm_scale, void* o_out, float* lse_out,
+                         void* stream);
+
 /* Self-test of the tensor-core building blocks (TMA tile load, shared-memory and TMEM operand
  * descriptors, TMEM load/store): runs one 128 x N x K product in the operand arrangement `mode`
  * and writes D (fp32 [128,N]) to `d_out`. a/b are device buffers in the arrangement the mode

@@ -20,6 +20,7 @@ _DTYPE = {torch.bfloat16: LVX_BF16, torch.float16: LVX_FP16, torch.float32: LVX_
 SYMBOLS = [
     "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_query_workspace", "lvx_fwd_block",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
+    "lvx_fwd_block_static",
 ]
 
 
@@ -57,6 +58,7 @@ def load():
                                   ctypes.c_size_t, vp]
     lib.lvx_add_cast.argtypes = [fp, fp, vp, ctypes.c_int, ctypes.c_size_t, vp]
     lib.lvx_selftest_mma.argtypes = [ctypes.c_int, vp, vp, fp, vp]
+    lib.lvx_fwd_block_static.argtypes = [sp, vp, vp, vp, i32p, ctypes.c_float, vp, fp, vp]
     for name in SYMBOLS:
         getattr(lib, name)  # AttributeError here means header and library disagree
         if name != "lvx_last_error":

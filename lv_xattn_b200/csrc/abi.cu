@@ -104,6 +104,11 @@ static int check_shape(const lvx_shape* s, const char* who) {
   return LVX_OK;
 }
 
+// Non-static doors for the other translation units of the library.
+int* device_status_ptr() { return status_ptr(); }
+int validate_shape(const lvx_shape* s, const char* who) { return check_shape(s, who); }
+int validate_arch() { return check_arch(); }
+
 #define LVX_REQUIRE_PTR(p, who)                                           \
   do {                                                                    \
     if (!(p)) return lvx::fail(LVX_ERR_NULL, "%s: %s is NULL", who, #p);  \

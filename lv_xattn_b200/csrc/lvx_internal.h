@@ -19,6 +19,11 @@ int make_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t dim0, u
                  uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1,
                  bool swizzle_atom_32b = false);
 
+// Device status word of the current device (nullptr if it cannot be resolved), and the ABI's argument checks.
+int* device_status_ptr();
+int validate_shape(const lvx_shape* s, const char* who);
+int validate_arch();
+
 inline int elt_size(int dtype) { return dtype == LVX_FP32 ? 4 : 2; }
 
 // Split-KV plan of the forward block; shared by the kernel launcher, the combine kernel and

@@ -1,0 +1,78 @@
+"""Generates tests/golden/ref_lvxattn_w{W}.npz from the REFERENCE's own implementation of the path.
+
+Runs the reference's `lv_xattn._attn_forward` / `_attn_backward` (its Triton kernels under Triton's CPU
+interpreter, its own step loop and P2P layer over gloo CPU ranks) on seeded inputs drawn with the reference
+benchmark's protocol (test.py:101-107) and sharded as test.py:164-178. Only runs where the reference checkout
+is present; the fixtures it writes are committed and are what tests/test_oracle.py reads.
+
+    python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 2
+
+Three shims touch no reference file: the process group is created with gloo before
+`lv_xattn.initialize_distributed()` (which then skips its NCCL init, async_communication.py:39-45),
+`torch.cuda.synchronize` is a no-op, and the backward autotuner is pinned to its first config so that it
+does not try to time kernels on a GPU.
+"""
+import argparse
+import math
+import os
+import sys
+
+import numpy as np
+
+
+def worker(rank, world, ref, port, out_dir):
+    os.environ.update(TRITON_INTERPRET="1", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, ref)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize = lambda *a, **k: None
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import lv_xattn
+    assert os.path.realpath(lv_xattn.__file__).startswith(os.path.realpath(ref)), lv_xattn.__file__
+    lv_xattn.initialize_distributed()
+    from lv_xattn import flash_attn_kernels as fk
+    fk._bwd_kernel.configs = fk._bwd_kernel.configs[0:1]
+
+    B, H, D = 1, 2, 128
+    Sq, Skv = 32 * world, 128 * world
+    torch.manual_seed(1)                                         # test.py:101
+    q = torch.empty(B, H, Sq, D, dtype=torch.float16).normal_(0.0, 0.5)
+    k = torch.empty(B, H, Skv, D, dtype=torch.float16).normal_(0.0, 0.5)
+    v = torch.empty(B, H, Skv, D, dtype=torch.float16).normal_(0.0, 0.5)
+    do = torch.randn(B, H, Sq, D).half()
+    scale = 1.0 / math.sqrt(D)
+
+    def sl(x, n):
+        return x[:, :, rank * n:(rank + 1) * n].contiguous()
+
+    ql, dol, kl, vl = sl(q, Sq // world), sl(do, Sq // world), sl(k, Skv // world), sl(v, Skv // world)
+    _, _, _, o, L = lv_xattn._attn_forward(ql, kl, vl, False, scale, None)
+    o, L = o.clone(), L.clone()
+    dq, dk, dv = lv_xattn._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash")
+    outs = {"o": o, "L": L, "dq": dq, "dk": dk, "dv": dv}
+    gathered = {}
+    for name, t in outs.items():
+        t = t.contiguous().float()
+        bufs = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(bufs, t)
+        gathered[name] = torch.stack(bufs).numpy()               # [W, ...] per-rank shards
+    if rank == 0:
+        np.savez_compressed(os.path.join(out_dir, f"ref_lvxattn_w{world}.npz"),
+                            q=q.numpy(), k=k.numpy(), v=v.numpy(), do=do.numpy(), scale=np.float32(scale),
+                            world=np.int32(world), **{f"ref_{n}": a.astype(np.float16 if n != "L" else np.float32)
+                                                      for n, a in gathered.items()})
+        print("wrote", f"ref_lvxattn_w{world}.npz")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", required=True, help="path of the reference checkout (uw-mad-dash/LV-XAttn)")
+    ap.add_argument("--world", type=int, default=1)
+    ap.add_argument("--port", type=int, default=29533)
+    a = ap.parse_args()
+    import torch.multiprocessing as mp
+    out = os.path.dirname(os.path.abspath(__file__))
+    mp.spawn(worker, args=(a.world, a.ref, a.port, out), nprocs=a.world, join=True)

@@ -20,3 +20,10 @@ from .attn import (  # noqa: F401
     attention,
     create_attention_class,
 )
+from .hf_patch import (  # noqa: F401,E402
+    clear_global_cross_attention_states,
+    get_global_cross_attention_states,
+    patch_cross_attention_forward,
+    patch_self_attention_forward,
+    set_global_cross_attention_states,
+)

@@ -88,3 +88,78 @@ def test_step_loop_bf16_gqa_key_padding():
 
 def test_step_loop_no_overlap():
     _run(2, (1, 2, 2, 32, 128, torch.float32, None, {"no_overlap": True}))
+
+
+def _hf_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    import copy
+    import _stub_ops
+    import lv_xattn_b200.attn as attn
+    from lv_xattn_b200 import async_communication as ac, hf_patch
+    from transformers.models.mllama import modeling_mllama as mllama
+    attn.ops = _stub_ops
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ac.initialize_distributed()
+    try:
+        cfg = mllama.MllamaTextConfig(hidden_size=256, num_attention_heads=2, num_key_value_heads=1,
+                                      num_hidden_layers=2, intermediate_size=512, vocab_size=64)
+        cfg._attn_implementation = "eager"
+        torch.manual_seed(0)
+        cross = mllama.MllamaTextCrossAttention(cfg, layer_idx=0)
+        selfa = mllama.MllamaTextSelfAttention(cfg, layer_idx=1)
+        rope = mllama.MllamaRotaryEmbedding(cfg)
+        S, Skv = 16 * world, 48 * world
+        x = torch.randn(1, S, 256)
+        states = torch.randn(1, Skv, 256)
+        g = torch.randn(1, S, 256)
+        pos = torch.arange(S)[None]
+        cos, sin = rope(x, pos)
+        causal = torch.full((S, S), float("-inf")).triu(1)[None, None]
+        xr = x.clone().requires_grad_(True)
+        ref_c, _ = cross(xr, cross_attention_states=states)
+        ref_s, _ = selfa(xr, attention_mask=causal, position_embeddings=(cos, sin))
+        (ref_c + ref_s).backward(g)
+        n, m = S // world, Skv // world
+        sl = slice(rank * n, (rank + 1) * n)
+        pc, ps = copy.deepcopy(cross), copy.deepcopy(selfa)
+        for p_ in list(pc.parameters()) + list(ps.parameters()):
+            p_.grad = None
+        pc.forward = hf_patch.patch_cross_attention_forward("lv_xattn").__get__(pc)
+        ps.forward = hf_patch.patch_self_attention_forward("lv_xattn").__get__(ps)
+        xl = x[:, sl].clone().requires_grad_(True)
+        hf_patch.set_global_cross_attention_states(states[:, rank * m:(rank + 1) * m].contiguous())
+        out_c, _ = pc(xl)
+        out_s, _ = ps(xl, attention_mask=None, position_embeddings=(cos[:, sl], sin[:, sl]))
+        (out_c + out_s).backward(g[:, sl])
+        hf_patch.clear_global_cross_attention_states()
+        ok = torch.allclose(out_c, ref_c[:, sl], atol=5e-5, rtol=1e-3) and torch.allclose(out_s, ref_s[:, sl], atol=5e-5, rtol=1e-3)
+        ok = ok and torch.allclose(xl.grad, xr.grad[:, sl], atol=1e-4, rtol=1e-3)
+        # weight gradients are partial sums per rank: reduce and compare with the unsharded ones
+        for (name, p_), (_, pr) in zip(list(pc.named_parameters()) + list(ps.named_parameters()),
+                                       list(cross.named_parameters()) + list(selfa.named_parameters())):
+            gsum = p_.grad.clone()
+            dist.all_reduce(gsum)
+            if not torch.allclose(gsum, pr.grad, atol=2e-4, rtol=1e-3):
+                ok = False
+                ret[rank] = ("bad", name, (gsum - pr.grad).abs().max().item())
+        if ok:
+            ret[rank] = ("ok",)
+        elif rank not in ret:
+            ret[rank] = ("bad", "outputs")
+    except Exception:
+        import traceback
+        ret[rank] = ("exc", traceback.format_exc())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_hf_hooks_sharded_over_two_ranks():
+    pytest.importorskip("transformers.models.mllama.modeling_mllama")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_hf_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        assert ret.get(r, ("missing",))[0] == "ok", f"rank {r}: {ret.get(r)}"

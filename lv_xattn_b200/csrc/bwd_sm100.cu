@@ -442,8 +442,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
                      const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                      float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st) {
-  if (s.dtype == LVX_FP32) return fail(LVX_ERR_DTYPE, "lvx_bwd_block: fp32 inputs are not built yet");
   if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "lvx_bwd_block: sm_scale must be positive");
+  if (s.dtype == LVX_FP32)
+    return launch_bwd_block_fp32(s, q, d_o, lse, delta, k, v, kv_valid_len, sm_scale, dq_acc, dk_acc, dv_acc,
+                                 accumulate_dkdv, st);
   const int g = s.Hq / s.Hkv;
   const int rows = g * s.Sq;
   const int es = elt_size(s.dtype);

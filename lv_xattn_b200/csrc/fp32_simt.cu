@@ -1,0 +1,348 @@
+// fp32 inputs: forward and backward flash-attention blocks on the FP32 FMA pipe, exact fp32 arithmetic.
+//
+// Why not tf32 on the tensor cores: for 32-bit operands tcgen05 wants K-major tiles in the 16-byte-unit
+// 128B swizzle and MN-major tiles in the 32-byte-unit swizzle. In the backward block every streamed tile
+// (Q, dO, and the resident K) is consumed both ways, so each would have to sit in shared memory twice, which
+// does not fit; and tf32 rounding (2^-11 per operand) leaves little margin under the 1e-4 bar the fp32 case
+// is held to. fp32 is the correctness configuration, not the throughput one, so it gets straightforward
+// tiled kernels with the same interface, workspace layout and masking rules as the 16-bit tensor-core path.
+//
+// Both kernels use 64 x 64 score tiles and 256 threads laid out 16 x 16: thread (ty, tx) owns the 4 x 4 block
+// of scores at rows 4*ty.., columns 4*tx.., and for the 64 x 128 products the rows 4*ty.. and the columns
+// tx + 16*c (c = 0..7), which makes every shared-memory access of a warp conflict-free or a broadcast.
+#include "lvx_internal.h"
+#include <math.h>
+
+namespace lvx {
+
+constexpr int SM_T = 64;            // tile edge
+constexpr int SM_LD = 129;          // padded row stride of a [64][128] tile
+constexpr int SM_LDP = 65;          // padded row stride of a [64][64] tile
+constexpr int SM_TILE = SM_T * SM_LD;
+constexpr int SM_PTILE = SM_T * SM_LDP;
+
+// Loads rows [row0, row0+64) of a dense [nrows, 128] fp32 matrix into a padded tile; rows past nrows are zero.
+__device__ __forceinline__ void load_tile(float* dst, const float* src, int row0, int nrows, int tid) {
+  for (int idx = tid; idx < SM_T * 128; idx += 256) {
+    const int r = idx >> 7, c = idx & 127;
+    const int gr = row0 + r;
+    dst[r * SM_LD + c] = gr < nrows ? src[size_t(gr) * 128 + c] : 0.f;
+  }
+}
+
+struct Fp32FwdParams {
+  const float *q, *k, *v;
+  const int32_t* kv_valid_len;
+  int rows, skv, hkv, nsplit, tiles_per_split;   // tiles_per_split counts 128-row tiles, as in the 16-bit plan
+  float scale_log2;
+  float *o_part, *ml_part;
+};
+
+__global__ void __launch_bounds__(256)
+fp32_fwd_kernel(const Fp32FwdParams p) {
+  extern __shared__ float sm[];
+  float* sQ = sm;
+  float* sK = sQ + SM_TILE;
+  float* sV = sK + SM_TILE;
+  float* sP = sV + SM_TILE;
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int mb = blockIdx.x, slab = blockIdx.y, split = blockIdx.z;
+  const int batch = slab / p.hkv;
+  int valid = p.skv;
+  if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
+  const int kv_begin = min(valid, split * p.tiles_per_split * 128);
+  const int kv_end = min(valid, (split + 1) * p.tiles_per_split * 128);
+  const float* qs = p.q + size_t(slab) * p.rows * 128;
+  const float* ks = p.k + size_t(slab) * p.skv * 128;
+  const float* vs = p.v + size_t(slab) * p.skv * 128;
+
+  load_tile(sQ, qs, mb * SM_T, p.rows, tid);
+  float m[4], l[4], o[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    m[i] = -INFINITY;
+    l[i] = 0.f;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) o[i][c] = 0.f;
+  }
+  for (int kv0 = kv_begin; kv0 < kv_end; kv0 += SM_T) {
+    __syncthreads();
+    load_tile(sK, ks, kv0, p.skv, tid);
+    load_tile(sV, vs, kv0, p.skv, tid);
+    __syncthreads();
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+    for (int d = 0; d < 128; ++d) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = sQ[(ty * 4 + i) * SM_LD + d];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = sK[(tx * 4 + j) * SM_LD + d];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = fmaf(a[i], b[j], s[i][j]);
+    }
+    // online softmax in base 2; a row is spread over the 16 threads that share ty
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s[i][j] = (kv0 + tx * 4 + j < kv_end) ? s[i][j] * p.scale_log2 : -INFINITY;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float m_new = fmaxf(m[i], mx);
+      const float moff = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m[i] - moff);       // m = -inf -> 0
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float pv = exp2f(s[i][j] - moff);
+        sum += pv;
+        sP[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv;
+      }
+#pragma unroll
+      for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      l[i] = l[i] * alpha + sum;
+      m[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) o[i][c] *= alpha;
+    }
+    __syncthreads();
+    for (int j = 0; j < SM_T; ++j) {
+      float pr[4], vv[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) pr[i] = sP[(ty * 4 + i) * SM_LDP + j];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) vv[c] = sV[j * SM_LD + tx + 16 * c];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) o[i][c] = fmaf(pr[i], vv[c], o[i][c]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = mb * SM_T + ty * 4 + i;
+    if (row >= p.rows) continue;
+    const size_t prow = (size_t(slab) * p.nsplit + split) * p.rows + row;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) p.o_part[prow * 128 + tx + 16 * c] = o[i][c];
+    if (tx == 0) {
+      p.ml_part[prow * 2] = m[i];
+      p.ml_part[prow * 2 + 1] = l[i];
+    }
+  }
+}
+
+struct Fp32BwdParams {
+  const float *q, *d_o, *lse, *delta, *k, *v;
+  const int32_t* kv_valid_len;
+  int rows, skv, hkv;
+  float scale, scale_log2;
+  float *dq_acc, *dk_acc, *dv_acc;
+  int accumulate;
+};
+
+__global__ void __launch_bounds__(256)
+fp32_bwd_kernel(const Fp32BwdParams p) {
+  extern __shared__ float sm[];
+  float* sK = sm;
+  float* sV = sK + SM_TILE;
+  float* sQ = sV + SM_TILE;
+  float* sDO = sQ + SM_TILE;
+  float* sP = sDO + SM_TILE;     // [q][kv]
+  float* sDS = sP + SM_PTILE;    // [q][kv]
+  const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+  const int kv0 = blockIdx.x * SM_T, slab = blockIdx.y;
+  const int batch = slab / p.hkv;
+  int valid = p.skv;
+  if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
+  const float* qs = p.q + size_t(slab) * p.rows * 128;
+  const float* dos = p.d_o + size_t(slab) * p.rows * 128;
+  const float* lses = p.lse + size_t(slab) * p.rows;
+  const float* deltas = p.delta + size_t(slab) * p.rows;
+  float* dqs = p.dq_acc + size_t(slab) * p.rows * 128;
+
+  load_tile(sK, p.k + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
+  load_tile(sV, p.v + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
+  float dk[4][8], dv[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) dk[i][c] = dv[i][c] = 0.f;
+
+  const bool live = kv0 < valid;
+  for (int q0 = 0; live && q0 < p.rows; q0 += SM_T) {
+    __syncthreads();
+    load_tile(sQ, qs, q0, p.rows, tid);
+    load_tile(sDO, dos, q0, p.rows, tid);
+    __syncthreads();
+    float s[4][4], dp[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = dp[i][j] = 0.f;
+    for (int d = 0; d < 128; ++d) {
+      float a[4], g[4], b[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = sQ[(ty * 4 + i) * SM_LD + d];
+        g[i] = sDO[(ty * 4 + i) * SM_LD + d];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        b[j] = sK[(tx * 4 + j) * SM_LD + d];
+        w[j] = sV[(tx * 4 + j) * SM_LD + d];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          s[i][j] = fmaf(a[i], b[j], s[i][j]);
+          dp[i][j] = fmaf(g[i], w[j], dp[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qrow = q0 + ty * 4 + i;
+      float l2 = INFINITY, dl = 0.f;      // +inf: rows that do not exist, or that have no valid key anywhere
+      if (qrow < p.rows) {
+        l2 = lses[qrow] * 1.4426950408889634f;
+        if (l2 == -INFINITY) l2 = INFINITY;
+        dl = deltas[qrow];
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool ok = kv0 + tx * 4 + j < valid;
+        const float pv = ok ? exp2f(s[i][j] * p.scale_log2 - l2) : 0.f;
+        sP[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv;
+        sDS[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv * (dp[i][j] - dl);
+      }
+    }
+    __syncthreads();
+    // dV[kv][d] += sum_q P[q][kv] dO[q][d];  dK[kv][d] += sum_q dS[q][kv] Q[q][d]   (this thread: kv rows 4*ty.., d = tx+16c)
+    for (int qi = 0; qi < SM_T; ++qi) {
+      float pr[4], dsr[4], g[8], a[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pr[i] = sP[qi * SM_LDP + ty * 4 + i];
+        dsr[i] = sDS[qi * SM_LDP + ty * 4 + i];
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        g[c] = sDO[qi * SM_LD + tx + 16 * c];
+        a[c] = sQ[qi * SM_LD + tx + 16 * c];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          dv[i][c] = fmaf(pr[i], g[c], dv[i][c]);
+          dk[i][c] = fmaf(dsr[i], a[c], dk[i][c]);
+        }
+    }
+    // dQ[q][d] = sum_kv dS[q][kv] K[kv][d]    (this thread: q rows 4*ty.., d = tx+16c)
+    float dq[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) dq[i][c] = 0.f;
+    for (int j = 0; j < SM_T; ++j) {
+      float dsr[4], b[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dsr[i] = sDS[(ty * 4 + i) * SM_LDP + j];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) b[c] = sK[j * SM_LD + tx + 16 * c];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) dq[i][c] = fmaf(dsr[i], b[c], dq[i][c]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int qrow = q0 + ty * 4 + i;
+      if (qrow < p.rows)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) atomicAdd(dqs + size_t(qrow) * 128 + tx + 16 * c, dq[i][c] * p.scale);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = kv0 + ty * 4 + i;
+    if (row >= p.skv) continue;
+    if (!live && p.accumulate) continue;
+    float* dkp = p.dk_acc + (size_t(slab) * p.skv + row) * 128;
+    float* dvp = p.dv_acc + (size_t(slab) * p.skv + row) * 128;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const int d = tx + 16 * c;
+      const float a = dk[i][c] * p.scale, b = dv[i][c];
+      dkp[d] = p.accumulate ? dkp[d] + a : a;
+      dvp[d] = p.accumulate ? dvp[d] + b : b;
+    }
+  }
+}
+
+int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, const void* k, const void* v,
+                          const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, cudaStream_t st) {
+  Fp32FwdParams p;
+  p.q = static_cast<const float*>(q);
+  p.k = static_cast<const float*>(k);
+  p.v = static_cast<const float*>(v);
+  p.kv_valid_len = kv_valid_len;
+  p.rows = pl.rows;
+  p.skv = s.Skv;
+  p.hkv = s.Hkv;
+  p.nsplit = pl.nsplit;
+  p.tiles_per_split = pl.tiles_per_split;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.o_part = o_part;
+  p.ml_part = ml_part;
+  const int smem = (3 * SM_TILE + SM_PTILE) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(fp32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 fwd)");
+  dim3 grid((pl.rows + SM_T - 1) / SM_T, s.B * s.Hkv, pl.nsplit);
+  fp32_fwd_kernel<<<grid, 256, smem, st>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "fp32_fwd_kernel launch");
+  return LVX_OK;
+}
+
+int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
+                          const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
+                          float* dk_acc, float* dv_acc, int accumulate_dkdv, cudaStream_t st) {
+  Fp32BwdParams p;
+  p.q = static_cast<const float*>(q);
+  p.d_o = static_cast<const float*>(d_o);
+  p.lse = lse;
+  p.delta = delta;
+  p.k = static_cast<const float*>(k);
+  p.v = static_cast<const float*>(v);
+  p.kv_valid_len = kv_valid_len;
+  p.rows = (s.Hq / s.Hkv) * s.Sq;
+  p.skv = s.Skv;
+  p.hkv = s.Hkv;
+  p.scale = sm_scale;
+  p.scale_log2 = sm_scale * 1.4426950408889634f;
+  p.dq_acc = dq_acc;
+  p.dk_acc = dk_acc;
+  p.dv_acc = dv_acc;
+  p.accumulate = accumulate_dkdv;
+  const int smem = (4 * SM_TILE + 2 * SM_PTILE) * sizeof(float);
+  cudaError_t e = cudaFuncSetAttribute(fp32_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 bwd)");
+  dim3 grid((s.Skv + SM_T - 1) / SM_T, s.B * s.Hkv, 1);
+  fp32_bwd_kernel<<<grid, 256, smem, st>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "fp32_bwd_kernel launch");
+  return LVX_OK;
+}
+
+}  // namespace lvx

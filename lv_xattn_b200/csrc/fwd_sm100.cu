@@ -389,8 +389,8 @@ FwdPlan plan_fwd(const lvx_shape& s) {
 int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const void* k, const void* v,
                      const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, int* status,
                      cudaStream_t st) {
-  if (s.dtype == LVX_FP32) return fail(LVX_ERR_DTYPE, "lvx_fwd_block: fp32 inputs are not built yet");
   if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "lvx_fwd_block: sm_scale must be positive");
+  if (s.dtype == LVX_FP32) return launch_fwd_block_fp32(s, pl, q, k, v, kv_valid_len, sm_scale, o_part, ml_part, st);
   (void)num_sms;
   CUtensorMap tmQ, tmK, tmV;
   const int es = elt_size(s.dtype);

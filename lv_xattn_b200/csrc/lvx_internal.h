@@ -50,6 +50,12 @@ int launch_bwd_prep(const lvx_shape& s, const void* o, const void* d_o, float* d
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
                      const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                      float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st);
+// fp32 inputs (exact FP32-FMA kernels, same workspace layout and masking rules as the tensor-core path)
+int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& p, const void* q, const void* k, const void* v,
+                          const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, cudaStream_t st);
+int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
+                          const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
+                          float* dk_acc, float* dv_acc, int accumulate_dkdv, cudaStream_t st);
 int launch_add_cast(const float* a, const float* b, void* out, int out_dtype, size_t n, cudaStream_t st);
 int launch_selftest(int mode, const void* a, const void* b, float* d_out, int* status, cudaStream_t st);
 

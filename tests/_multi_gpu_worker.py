@@ -19,6 +19,7 @@ scale = 1.0 / math.sqrt(128.0)
 cases = [
     (1, 8, 2, 128 * world, 1024 * world, torch.bfloat16, None),
     (2, 4, 2, 64 * world, 512 * world, torch.bfloat16, [512 * world, 512 * world * 3 // 4]),
+    (1, 8, 2, 64 * world, 512 * world, torch.float32, None),
 ]
 for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
     q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 31, dtype)
@@ -38,6 +39,9 @@ for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
         "dk": (dk.float().cpu() - orc.shard(dk_ref, rank, world)).abs().max().item(),
         "dv": (dv.float().cpu() - orc.shard(dv_ref, rank, world)).abs().max().item(),
     }
-    assert errs["lse"] <= 1e-3 and all(errs[n] <= 2e-2 for n in ("o", "dq", "dk", "dv")), (rank, errs)
+    if dtype == torch.float32:
+        assert all(e <= 1e-4 for e in errs.values()), (rank, errs)
+    else:
+        assert errs["lse"] <= 1e-3 and all(errs[n] <= 2e-2 for n in ("o", "dq", "dk", "dv")), (rank, errs)
 print(f"RANK_OK {rank}", flush=True)
 torch.distributed.destroy_process_group()

@@ -51,7 +51,10 @@ typedef struct lvx_shape {
   int32_t Skv;     /* key/value rows resident on this GPU    */
   int32_t D;       /* head dimension (128)                   */
   int32_t dtype;   /* enum lvx_dtype                         */
-  int32_t reserved;
+  int32_t q_blocks; /* number of query blocks that share each K/V batch entry; 0 or 1 = one.
+                     * With q_blocks = n the query-side tensors (q, dO, o, lse, delta, dq) carry a leading
+                     * block axis: [n, B, Hq, Sq, D] / [n, B*Hq, Sq]; block i of batch b attends K/V batch b.
+                     * Used to run the query blocks of all sequence-parallel ranks in one K/V pass. */
 } lvx_shape;
 
 /* Library / ABI version (LVX_ABI_VERSION). No reference counterpart (the reference is pure Python). */
@@ -109,6 +112,20 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
                   const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                   float* dk_acc, float* dv_acc, int accumulate_dkdv, void* workspace,
                   size_t workspace_bytes, void* stream);
+
+/* Merge of `count` finished partial results of the same query block, each computed against a different
+ * K/V shard: o_parts fp32 [count][B*Hq*Sq*D], lse_parts fp32 [count][B*Hq*Sq] -> o_out (shape.dtype) and
+ * lse_out, with the same stable log-sum-exp merge as lvx_fwd_combine_merge ((0,-inf) is the neutral
+ * element). part_stride_o / part_stride_lse are the distances, in floats, between consecutive partials.
+ * This is the reduce step of the all-blocks-per-pass schedule; in the reference the same merge happens
+ * one hop at a time in _rescale_kernel (lv_xattn/attn.py:37-110). */
+int lvx_fwd_merge_parts(const lvx_shape* s, const float* o_parts, const float* lse_parts, int count,
+                        size_t part_stride_o, size_t part_stride_lse, void* o_out, float* lse_out, void* stream);
+
+/* out[i] = (dtype) sum_{c < count} parts[c * part_stride + i] over n fp32 elements: the reduce step for
+ * dQ in the all-blocks-per-pass schedule (reference: lv_xattn/attn.py:527, one hop at a time). */
+int lvx_sum_cast(const float* parts, int count, size_t part_stride, void* out, int out_dtype, size_t n,
+                 void* stream);
 
 /* out[i] = (dtype) (a[i] + b[i]) over n fp32 elements; b may be NULL; out_dtype is an lvx_dtype
  * (LVX_FP32 keeps fp32). Used for: travelling dQ += local dQ, and the final down-cast of

@@ -20,12 +20,12 @@ _DTYPE = {torch.bfloat16: LVX_BF16, torch.float16: LVX_FP16, torch.float32: LVX_
 SYMBOLS = [
     "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_query_workspace", "lvx_fwd_block",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
-    "lvx_fwd_block_static",
+    "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
 ]
 
 
 class LvxShape(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_int32) for n in ("B", "Hq", "Hkv", "Sq", "Skv", "D", "dtype", "reserved")]
+    _fields_ = [(n, ctypes.c_int32) for n in ("B", "Hq", "Hkv", "Sq", "Skv", "D", "dtype", "q_blocks")]
 
 
 class LvxError(RuntimeError):
@@ -58,6 +58,8 @@ def load():
                                   ctypes.c_size_t, vp]
     lib.lvx_add_cast.argtypes = [fp, fp, vp, ctypes.c_int, ctypes.c_size_t, vp]
     lib.lvx_selftest_mma.argtypes = [ctypes.c_int, vp, vp, fp, vp]
+    lib.lvx_fwd_merge_parts.argtypes = [sp, fp, fp, ctypes.c_int, ctypes.c_size_t, ctypes.c_size_t, vp, fp, vp]
+    lib.lvx_sum_cast.argtypes = [fp, ctypes.c_int, ctypes.c_size_t, vp, ctypes.c_int, ctypes.c_size_t, vp]
     lib.lvx_fwd_block_static.argtypes = [sp, vp, vp, vp, i32p, ctypes.c_float, vp, fp, vp]
     for name in SYMBOLS:
         getattr(lib, name)  # AttributeError here means header and library disagree
@@ -81,10 +83,10 @@ def stream_ptr():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def make_shape(B, Hq, Hkv, Sq, Skv, D, dtype) -> LvxShape:
+def make_shape(B, Hq, Hkv, Sq, Skv, D, dtype, q_blocks=1) -> LvxShape:
     if dtype not in _DTYPE:
         raise ValueError(f"unsupported dtype {dtype}; expected bfloat16, float16 or float32")
-    return LvxShape(B, Hq, Hkv, Sq, Skv, D, _DTYPE[dtype], 0)
+    return LvxShape(B, Hq, Hkv, Sq, Skv, D, _DTYPE[dtype], q_blocks)
 
 
 def dtype_code(dtype) -> int:

@@ -180,6 +180,44 @@ def send_recv_bwd_rescale_reqs(dq_send, dq_recv, comm_mode):
     return _exchange([dq_send], [dq_recv], comm_mode)
 
 
+def p2p_all_gather(local_tensors, gathered, comm_mode):
+    """gathered[i][s] <- rank s's local_tensors[i] for every rank s (the own slot is a local copy).
+    One batch of P2P sends/receives: every peer pair exchanges directly over NVSwitch, which moves the same
+    bytes as W-1 ring hops in one launch."""
+    group = get_sequence_parallel_group()
+    r, w = get_sequence_parallel_rank(), get_sequence_parallel_size()
+    ops_ = []
+    for s in range(w):
+        if s != r:
+            for g in gathered:
+                ops_.append(P2POp(op=irecv, tensor=g[s], peer=s, group=group))
+    for s in range(w):
+        if s != r:
+            for t in local_tensors:
+                ops_.append(P2POp(op=isend, tensor=t, peer=s, group=group))
+    for t, g in zip(local_tensors, gathered):
+        g[r].copy_(t)
+    return [launch_async_handles(ops_, comm_mode)]
+
+
+def p2p_all_to_all(pairs, comm_mode):
+    """For every (send, recv) pair of [W, ...] tensors: send[s] goes to rank s, recv[s] comes from rank s."""
+    group = get_sequence_parallel_group()
+    r, w = get_sequence_parallel_rank(), get_sequence_parallel_size()
+    ops_ = []
+    for s in range(w):
+        if s != r:
+            for _, rv in pairs:
+                ops_.append(P2POp(op=irecv, tensor=rv[s], peer=s, group=group))
+    for s in range(w):
+        if s != r:
+            for sd, _ in pairs:
+                ops_.append(P2POp(op=isend, tensor=sd[s], peer=s, group=group))
+    for sd, rv in pairs:
+        rv[r].copy_(sd[r])
+    return [launch_async_handles(ops_, comm_mode)]
+
+
 def launch_async_handles(handles, comm_mode):
     if comm_mode == "nocomm":
         return []

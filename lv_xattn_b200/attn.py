@@ -19,6 +19,8 @@ count (no expansion, :392-393), and key padding is a per-batch valid length inst
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import ops
@@ -27,6 +29,8 @@ from .async_communication import (
     get_sequence_parallel_rank,
     get_sequence_parallel_size,
     get_slabs,
+    p2p_all_gather,
+    p2p_all_to_all,
     reset_global_memory_buffer,
     send_recv_bwd_comp_reqs,
     send_recv_bwd_rescale_reqs,
@@ -36,6 +40,17 @@ from .async_communication import (
 )
 
 _SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
+
+
+def _schedule(schedule):
+    """"gather" (default): every rank fetches all W query blocks, makes ONE pass over its K/V shard and the
+    partial results are exchanged and reduced at home -- one kernel launch per pass, dK/dV written once.
+    "ring": the reference's step loop, one query block per step with travelling accumulators
+    (lv_xattn/attn.py:364-429). Both move the same bytes per GPU; LVX_SCHEDULE overrides the default."""
+    s = schedule or os.environ.get("LVX_SCHEDULE", "gather")
+    if s not in ("gather", "ring"):
+        raise ValueError(f"unknown schedule {s!r}")
+    return s
 
 
 def _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args):
@@ -82,7 +97,7 @@ def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> torch.Tensor:
 
 
 def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bias_args=[], remote_bias_args=[],
-                  no_overlap=False, kv_valid_len=None):
+                  no_overlap=False, kv_valid_len=None, schedule=None):
     """Returns (q, k, v, o, L): o like q, L fp32 [B*Hq, Sq_local] natural-log lse (reference :297-435).
 
     comm_mode == "nocomm" runs the W-step schedule without any transfer (timing ablation, as in the
@@ -105,6 +120,21 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         return q, k, v, o, L
 
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
+    if _schedule(schedule) == "gather":
+        q_all = _carve(get_slabs("g_q", W * n_o * es, dev, 1)[0], 0, (W, B, Hq, Sq, D), dt)
+        wait_async_handles(p2p_all_gather([qc], [q_all], comm_mode))
+        part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl)
+        sbuf = get_slabs("g_acc_send", W * (n_o + n_l) * 4, dev, 1)[0]
+        rbuf = get_slabs("g_acc_recv", W * (n_o + n_l) * 4, dev, 1)[0]
+        o_parts = _carve(sbuf, 0, (W, B, Hq, Sq, D), torch.float32)
+        l_parts = _carve(sbuf, W * n_o * 4, (W, B * Hq, Sq), torch.float32)
+        o_recv = _carve(rbuf, 0, (W, B, Hq, Sq, D), torch.float32)
+        l_recv = _carve(rbuf, W * n_o * 4, (W, B * Hq, Sq), torch.float32)
+        ops.fwd_combine(part, None, None, o_parts, l_parts.view(W * B * Hq, Sq), False)
+        wait_async_handles(p2p_all_to_all([(o_parts, o_recv), (l_parts, l_recv)], comm_mode))
+        ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
+        return q, k, v, o, L
+
     acc_bytes = n_o * 4 + n_l * 4
     q_bufs = get_slabs("fwd_q", n_o * es, dev, 2)
     send_bufs = get_slabs("fwd_acc_send", acc_bytes, dev, 2)
@@ -156,7 +186,7 @@ def _exchange_final(o_send, l_send, o_recv, l_recv, comm_mode):
 
 
 def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engine, bias_func=None,
-                   local_bias_args=[], remote_bias_args=[], no_overlap=False, kv_valid_len=None):
+                   local_bias_args=[], remote_bias_args=[], no_overlap=False, kv_valid_len=None, schedule=None):
     """Returns (dq, dk, dv): dq like q, dk/dv like k/v (summed over the query heads of each KV group)
     (reference :437-545). `backward_engine` is accepted and ignored, as in the reference."""
     _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args)
@@ -184,6 +214,20 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             dq_acc.zero_()
             ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk_acc, dv_acc, False, kvl)
         ops.add_cast(dq_acc, None, dt, out=dq)
+    elif _schedule(schedule) == "gather":
+        gbuf = get_slabs("g_bwd_in", W * (2 * n_q * es + 2 * n_r * 4), dev, 1)[0]
+        q_all = _carve(gbuf, 0, (W, B, Hq, Sq, D), dt)
+        do_all = _carve(gbuf, W * n_q * es, (W, B, Hq, Sq, D), dt)
+        l_all = _carve(gbuf, 2 * W * n_q * es, (W, B * Hq, Sq), torch.float32)
+        d_all = _carve(gbuf, 2 * W * n_q * es + W * n_r * 4, (W, B * Hq, Sq), torch.float32)
+        wait_async_handles(p2p_all_gather([qc, doc, Lc, delta], [q_all, do_all, l_all, d_all], comm_mode))
+        dq_parts = _carve(get_slabs("g_dq_send", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
+        dq_recv = _carve(get_slabs("g_dq_recv", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
+        dq_parts.zero_()
+        ops.bwd_block(q_all, do_all, l_all.view(W * B * Hq, Sq), d_all.view(W * B * Hq, Sq), kc, vc, sm_scale,
+                      dq_parts, dk_acc, dv_acc, False, kvl)
+        wait_async_handles(p2p_all_to_all([(dq_parts, dq_recv)], comm_mode))
+        ops.sum_cast(dq_recv, dt, out=dq)
     else:
         slab_bytes = 2 * n_q * es + 2 * n_r * 4
         in_bufs = get_slabs("bwd_in", slab_bytes, dev, 3)

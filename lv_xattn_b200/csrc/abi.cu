@@ -99,7 +99,9 @@ static int check_shape(const lvx_shape* s, const char* who) {
   if (s->Hq % s->Hkv) return fail(LVX_ERR_SHAPE, "%s: Hq=%d is not a multiple of Hkv=%d", who, s->Hq, s->Hkv);
   if (s->dtype != LVX_BF16 && s->dtype != LVX_FP16 && s->dtype != LVX_FP32)
     return fail(LVX_ERR_DTYPE, "%s: dtype %d unsupported", who, s->dtype);
-  if (int64_t(s->Hq / s->Hkv) * s->Sq > (int64_t(1) << 30) || int64_t(s->B) * s->Hkv > 65535)
+  if (s->q_blocks < 0 || s->q_blocks > 4096) return fail(LVX_ERR_SHAPE, "%s: q_blocks %d out of range", who, s->q_blocks);
+  if (int64_t(s->Hq / s->Hkv) * s->Sq > (int64_t(1) << 30) ||
+      int64_t(s->q_blocks > 1 ? s->q_blocks : 1) * s->B * s->Hkv > 65535)
     return fail(LVX_ERR_SHAPE, "%s: dimension too large", who);
   return LVX_OK;
 }
@@ -224,6 +226,32 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
   if (!sp) return fail(LVX_ERR_DRIVER, "%s: status word unavailable", who);
   return launch_bwd_block(*s, q, d_o, lse, delta, k, v, kv_valid_len, sm_scale, dq_acc, dk_acc, dv_acc,
                           accumulate_dkdv, sp, static_cast<cudaStream_t>(stream));
+}
+
+int lvx_fwd_merge_parts(const lvx_shape* s, const float* o_parts, const float* lse_parts, int count,
+                        size_t part_stride_o, size_t part_stride_lse, void* o_out, float* lse_out, void* stream) {
+  const char* who = "lvx_fwd_merge_parts";
+  int rc = check_shape(s, who);
+  if (rc) return rc;
+  LVX_REQUIRE_PTR(o_parts, who);
+  LVX_REQUIRE_PTR(lse_parts, who);
+  LVX_REQUIRE_PTR(o_out, who);
+  LVX_REQUIRE_PTR(lse_out, who);
+  if (count < 1 || (part_stride_o & 3) != 0) return fail(LVX_ERR_SHAPE, "%s: count must be >= 1 and the O stride a multiple of 4 floats", who);
+  return launch_fwd_merge_parts(*s, o_parts, lse_parts, count, part_stride_o, part_stride_lse, o_out, lse_out,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int lvx_sum_cast(const float* parts, int count, size_t part_stride, void* out, int out_dtype, size_t n, void* stream) {
+  const char* who = "lvx_sum_cast";
+  if (n == 0) return LVX_OK;
+  LVX_REQUIRE_PTR(parts, who);
+  LVX_REQUIRE_PTR(out, who);
+  if (count < 1 || (part_stride & 3) != 0 || (n & 3) != 0)
+    return fail(LVX_ERR_SHAPE, "%s: count >= 1, stride and n multiples of 4 floats are required", who);
+  if (out_dtype != LVX_BF16 && out_dtype != LVX_FP16 && out_dtype != LVX_FP32)
+    return fail(LVX_ERR_DTYPE, "%s: dtype %d unsupported", who, out_dtype);
+  return launch_sum_cast(parts, count, part_stride, out, out_dtype, n, static_cast<cudaStream_t>(stream));
 }
 
 int lvx_add_cast(const float* a, const float* b, void* out, int out_dtype, size_t n, void* stream) {

@@ -70,8 +70,10 @@ struct BwdParams {
   int rows;            // g * Sq
   int skv;
   int hkv;
+  int nblk;            // query blocks per K/V batch entry (query slab = kv slab + block * kv_slabs)
+  int kv_slabs;        // B*Hkv
   const int32_t* kv_valid_len;
-  const float* lse;    // [B*Hq*Sq]  == [slab][rows]
+  const float* lse;    // [nblk*B*Hq*Sq]  == [query slab][rows]
   const float* delta;
   float scale;         // sm_scale
   float scale_log2;    // sm_scale * log2(e)
@@ -112,7 +114,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
   const bool tile_live = kv0 < valid;          // at least one valid K/V row in this tile
   const bool tile_partial = valid < kv0 + 128; // some rows of the tile are padding
-  const int nq = (p.rows + 127) >> 7;
+  const int nq = (p.rows + 127) >> 7;         // 128-row tiles per query block
+  const int ntot = nq * p.nblk;               // tiles this CTA walks: all blocks, one after the other
   // The operand descriptors assume 1024-byte aligned tiles; refuse to run otherwise.
   const bool misaligned = (smem_u32(smem) & 1023u) != 0;
   if (misaligned && tid == 0) atomicCAS(p.status, 0, BWD_CODE(7, 0));
@@ -155,11 +158,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tX = tmem_base + TM_X + lane_sel, tY = tmem_base + TM_Y + lane_sel;
       const float c = p.scale_log2;
-      const size_t stat_base = size_t(slab) * p.rows;
-      float* dq_col = p.dq_acc + size_t(slab) * p.rows * 128 + r;   // + query_row * 128
+      // tile j -> (query slab, first row inside the block)
+      auto tile_slab = [&](int j) { return slab + (j / nq) * p.kv_slabs; };
+      auto tile_row0 = [&](int j) { return (j % nq) * 128; };
       // Per-column statistics of a query tile: threads 0-127 fetch lse, 128-255 delta (warps 0-7).
       auto fetch_stat = [&](int j) -> float {
-        const int qrow = j * 128 + (tid & 127);
+        const int qrow = tile_row0(j) + (tid & 127);
+        const size_t stat_base = size_t(tile_slab(j)) * p.rows;
         if (tid < 128) {
           float v = INFINITY;   // +inf => P = 0 for query rows that do not exist
           if (qrow < p.rows) {
@@ -179,11 +184,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (lane == 0) mbar_arrive(&bars[BB_STAT_FULL + (j & 1)]);
       };
       put_stat(0, fetch_stat(0));
-      float stat_next = nq > 1 ? fetch_stat(1) : 0.f;     // fetched two tiles ahead, published one ahead
+      float stat_next = ntot > 1 ? fetch_stat(1) : 0.f;   // fetched two tiles ahead, published one ahead
       bool alive = true;
-      for (int j = 0; j < nq; ++j) {
+      for (int j = 0; j < ntot; ++j) {
         float stat_after = 0.f;
-        if (j + 2 < nq) stat_after = fetch_stat(j + 2);
+        if (j + 2 < ntot) stat_after = fetch_stat(j + 2);
         if (warp == 0) BWD_TS(0, 0);
         if (!mbar_wait(&bars[BB_S_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL)) ||
             !mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL))) {
@@ -249,7 +254,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[BB_PDS_FULL]);
         if (warp == 0) BWD_TS(0, 4);
-        if (j + 1 < nq) put_stat(j + 1, stat_next);
+        if (j + 1 < ntot) put_stat(j + 1, stat_next);
         stat_next = stat_after;
         // ---- drain dQ^T of this tile: Y holds [head dim (lanes)][query (columns)] ----
         if (!mbar_wait(&bars[BB_DQ_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DQ_FULL))) {
@@ -266,9 +271,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);
         if (warp == 0) BWD_TS(0, 6);
         if (!(p.debug & 1)) {
-          const int q0 = j * 128 + cg * 32;
+          const int q0 = tile_row0(j) + cg * 32;
           const int ncols = min(32, p.rows - q0);
-          float* dst = dq_col + size_t(q0) * 128;
+          float* dst = p.dq_acc + (size_t(tile_slab(j)) * p.rows + q0) * 128 + r;
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (i < ncols) atomicAdd(dst + i * 128, __uint_as_float(dq[i]) * p.scale);
@@ -315,15 +320,16 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           tma_load_3d(smem + BWD_OFF_V + h * BWD_HALF, &tmV, &bars[BB_KV_FULL], h * 64, kv0, slab);
         }
         int issued = 0;
-        for (int j = 0; j < nq; ++j) {
+        for (int j = 0; j < ntot; ++j) {
           const int s = j % BWD_NSQ;
           const uint32_t ph = (j / BWD_NSQ) & 1;
+          const int qslab = slab + (j / nq) * p.kv_slabs, y = (j % nq) * 128;
           if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY))) break;
           uint8_t* dstq = smem + BWD_OFF_Q + s * 2 * BWD_TILE;
           mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_TILE);
           for (int h = 0; h < 2; ++h) {
-            tma_load_3d(dstq + h * BWD_HALF, &tmQ, &bars[BB_Q_FULL + s], h * 64, j * 128, slab);
-            tma_load_3d(dstq + BWD_TILE + h * BWD_HALF, &tmDO, &bars[BB_Q_FULL + s], h * 64, j * 128, slab);
+            tma_load_3d(dstq + h * BWD_HALF, &tmQ, &bars[BB_Q_FULL + s], h * 64, y, qslab);
+            tma_load_3d(dstq + BWD_TILE + h * BWD_HALF, &tmDO, &bars[BB_Q_FULL + s], h * 64, y, qslab);
           }
           issued = j + 1;
         }
@@ -382,7 +388,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           issue_st(tmem_base + TM_Y, sV, sQ0 + BWD_TILE);
           tc_commit(&bars[BB_DP_FULL]);
         }
-        for (int j = 0; ok && j < nq; ++j) {
+        for (int j = 0; ok && j < ntot; ++j) {
           const int s = j % BWD_NSQ;
           const uint32_t sQ = sQ0 + s * 2 * BWD_TILE, sDO = sQ + BWD_TILE;
           BWD_TS(1, 0);
@@ -397,7 +403,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           issue_acc(tmem_base + TM_DK, tmem_base + TM_X + 64, sQ, j == 0);
           tc_commit(&bars[BB_Q_EMPTY + s]);
           BWD_TS(1, 3);
-          if (j + 1 < nq) {
+          if (j + 1 < ntot) {
             const int s1 = (j + 1) % BWD_NSQ;
             const uint32_t sQ1 = sQ0 + s1 * 2 * BWD_TILE;
             ok = mbar_wait(&bars[BB_Q_FULL + s1], ((j + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL));
@@ -451,10 +457,11 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   const int es = elt_size(s.dtype);
   const uint64_t row_bytes = uint64_t(128) * es;
   const uint64_t slabs = uint64_t(s.B) * s.Hkv;
+  const int qb = q_blocks_of(s);
   CUtensorMap tmQ, tmDO, tmK, tmV;
   int rc;
-  if ((rc = make_tmap_3d(&tmQ, s.dtype, q, 128, rows, slabs, row_bytes, row_bytes * rows, 64, 128))) return rc;
-  if ((rc = make_tmap_3d(&tmDO, s.dtype, d_o, 128, rows, slabs, row_bytes, row_bytes * rows, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmQ, s.dtype, q, 128, rows, slabs * qb, row_bytes, row_bytes * rows, 64, 128))) return rc;
+  if ((rc = make_tmap_3d(&tmDO, s.dtype, d_o, 128, rows, slabs * qb, row_bytes, row_bytes * rows, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmK, s.dtype, k, 128, s.Skv, slabs, row_bytes, row_bytes * s.Skv, 64, 128))) return rc;
   if ((rc = make_tmap_3d(&tmV, s.dtype, v, 128, s.Skv, slabs, row_bytes, row_bytes * s.Skv, 64, 128))) return rc;
 
@@ -462,6 +469,8 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   p.rows = rows;
   p.skv = s.Skv;
   p.hkv = s.Hkv;
+  p.nblk = qb;
+  p.kv_slabs = int(slabs);
   p.kv_valid_len = kv_valid_len;
   p.lse = lse;
   p.delta = delta;

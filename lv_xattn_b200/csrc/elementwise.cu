@@ -119,7 +119,7 @@ fwd_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ m
 int launch_fwd_combine(const lvx_shape& s, const FwdPlan& p, const float* o_part, const float* ml_part,
                        const float* o_in, const float* lse_in, void* o_out, float* lse_out, int out_is_final,
                        cudaStream_t st) {
-  const long total_rows = long(s.B) * s.Hq * s.Sq;
+  const long total_rows = long(q_blocks_of(s)) * s.B * s.Hq * s.Sq;
   const int threads = 256;
   const long blocks = (total_rows * 32 + threads - 1) / threads;
   const int out = out_is_final ? s.dtype : LVX_FP32;
@@ -131,6 +131,52 @@ int launch_fwd_combine(const lvx_shape& s, const FwdPlan& p, const float* o_part
     fwd_combine_kernel<2><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_combine launch");
+  return LVX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Merge of `count` normalised partial results (O fp32, lse) of the same rows; one warp per row.
+template <int OUT>
+__global__ void __launch_bounds__(256)
+fwd_merge_parts_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int count,
+                       size_t stride_o, size_t stride_lse, void* __restrict__ o_out, float* __restrict__ lse_out,
+                       long total_rows) {
+  const int lane = threadIdx.x & 31;
+  const long row = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (row >= total_rows) return;
+  float mx = -INFINITY;
+  for (int c = 0; c < count; ++c) mx = fmaxf(mx, lse_parts[c * stride_lse + row]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float tot = 0.f;
+  if (mx != -INFINITY) {
+    for (int c = 0; c < count; ++c) {
+      const float l = lse_parts[c * stride_lse + row];
+      if (l == -INFINITY) continue;
+      const float w = expf(l - mx);
+      tot += w;
+      const float4 v = reinterpret_cast<const float4*>(o_parts + c * stride_o)[size_t(row) * 32 + lane];
+      acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
+    }
+    const float inv = 1.f / tot;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+  }
+  store4<OUT>(o_out, size_t(row) * 32 + lane, acc);
+  if (lane == 0) lse_out[row] = mx == -INFINITY ? -INFINITY : mx + logf(tot);
+}
+
+int launch_fwd_merge_parts(const lvx_shape& s, const float* o_parts, const float* lse_parts, int count,
+                           size_t stride_o, size_t stride_lse, void* o_out, float* lse_out, cudaStream_t st) {
+  const long total_rows = long(q_blocks_of(s)) * s.B * s.Hq * s.Sq;
+  const int threads = 256;
+  const long blocks = (total_rows * 32 + threads - 1) / threads;
+  if (s.dtype == LVX_BF16)
+    fwd_merge_parts_kernel<0><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows);
+  else if (s.dtype == LVX_FP16)
+    fwd_merge_parts_kernel<1><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows);
+  else
+    fwd_merge_parts_kernel<2><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "fwd_merge_parts launch");
   return LVX_OK;
 }
 
@@ -150,7 +196,7 @@ bwd_prep_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float*
 }
 
 int launch_bwd_prep(const lvx_shape& s, const void* o, const void* d_o, float* delta, cudaStream_t st) {
-  const long total_rows = long(s.B) * s.Hq * s.Sq;
+  const long total_rows = long(q_blocks_of(s)) * s.B * s.Hq * s.Sq;
   const int threads = 256;
   const long blocks = (total_rows * 32 + threads - 1) / threads;
   if (s.dtype == LVX_BF16) bwd_prep_kernel<0><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows);
@@ -195,6 +241,35 @@ int launch_add_cast(const float* a, const float* b, void* out, int out_dtype, si
   else add_cast_kernel<2><<<blocks, threads, 0, st>>>(a, b, out, n4, n);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "add_cast launch");
+  return LVX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int OUT>
+__global__ void __launch_bounds__(256)
+sum_cast_kernel(const float* __restrict__ parts, int count, size_t stride, void* __restrict__ out, size_t n4) {
+  const size_t gstride = size_t(gridDim.x) * blockDim.x;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += gstride) {
+    float4 v = reinterpret_cast<const float4*>(parts)[i];
+    for (int c = 1; c < count; ++c) {
+      const float4 w = reinterpret_cast<const float4*>(parts + c * stride)[i];
+      v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    store4<OUT>(out, i, v);
+  }
+}
+
+int launch_sum_cast(const float* parts, int count, size_t stride, void* out, int out_dtype, size_t n, cudaStream_t st) {
+  const size_t n4 = n / 4;
+  const int threads = 256;
+  size_t blocks = (n4 + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks == 0) blocks = 1;
+  if (out_dtype == LVX_BF16) sum_cast_kernel<0><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4);
+  else if (out_dtype == LVX_FP16) sum_cast_kernel<1><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4);
+  else sum_cast_kernel<2><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "sum_cast launch");
   return LVX_OK;
 }
 

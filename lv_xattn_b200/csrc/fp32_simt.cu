@@ -33,7 +33,7 @@ __device__ __forceinline__ void load_tile(float* dst, const float* src, int row0
 struct Fp32FwdParams {
   const float *q, *k, *v;
   const int32_t* kv_valid_len;
-  int rows, skv, hkv, nsplit, tiles_per_split;   // tiles_per_split counts 128-row tiles, as in the 16-bit plan
+  int rows, skv, hkv, kv_slabs, nsplit, tiles_per_split;   // tiles_per_split counts 128-row tiles, as in the 16-bit plan
   float scale_log2;
   float *o_part, *ml_part;
 };
@@ -47,14 +47,15 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
   float* sP = sV + SM_TILE;
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   const int mb = blockIdx.x, slab = blockIdx.y, split = blockIdx.z;
-  const int batch = slab / p.hkv;
+  const int kvs = slab % p.kv_slabs;          // several query blocks may share one K/V batch entry
+  const int batch = kvs / p.hkv;
   int valid = p.skv;
   if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
   const int kv_begin = min(valid, split * p.tiles_per_split * 128);
   const int kv_end = min(valid, (split + 1) * p.tiles_per_split * 128);
   const float* qs = p.q + size_t(slab) * p.rows * 128;
-  const float* ks = p.k + size_t(slab) * p.skv * 128;
-  const float* vs = p.v + size_t(slab) * p.skv * 128;
+  const float* ks = p.k + size_t(kvs) * p.skv * 128;
+  const float* vs = p.v + size_t(kvs) * p.skv * 128;
 
   load_tile(sQ, qs, mb * SM_T, p.rows, tid);
   float m[4], l[4], o[4][8];
@@ -144,7 +145,7 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
 struct Fp32BwdParams {
   const float *q, *d_o, *lse, *delta, *k, *v;
   const int32_t* kv_valid_len;
-  int rows, skv, hkv;
+  int rows, skv, hkv, nblk, kv_slabs;
   float scale, scale_log2;
   float *dq_acc, *dk_acc, *dv_acc;
   int accumulate;
@@ -164,11 +165,6 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
   const int batch = slab / p.hkv;
   int valid = p.skv;
   if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
-  const float* qs = p.q + size_t(slab) * p.rows * 128;
-  const float* dos = p.d_o + size_t(slab) * p.rows * 128;
-  const float* lses = p.lse + size_t(slab) * p.rows;
-  const float* deltas = p.delta + size_t(slab) * p.rows;
-  float* dqs = p.dq_acc + size_t(slab) * p.rows * 128;
 
   load_tile(sK, p.k + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
   load_tile(sV, p.v + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
@@ -179,7 +175,15 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
     for (int c = 0; c < 8; ++c) dk[i][c] = dv[i][c] = 0.f;
 
   const bool live = kv0 < valid;
-  for (int q0 = 0; live && q0 < p.rows; q0 += SM_T) {
+  const int tiles_per_block = (p.rows + SM_T - 1) / SM_T;
+  for (int it = 0; live && it < tiles_per_block * p.nblk; ++it) {
+    const int qslab = slab + (it / tiles_per_block) * p.kv_slabs;
+    const int q0 = (it % tiles_per_block) * SM_T;
+    const float* qs = p.q + size_t(qslab) * p.rows * 128;
+    const float* dos = p.d_o + size_t(qslab) * p.rows * 128;
+    const float* lses = p.lse + size_t(qslab) * p.rows;
+    const float* deltas = p.delta + size_t(qslab) * p.rows;
+    float* dqs = p.dq_acc + size_t(qslab) * p.rows * 128;
     __syncthreads();
     load_tile(sQ, qs, q0, p.rows, tid);
     load_tile(sDO, dos, q0, p.rows, tid);
@@ -300,6 +304,7 @@ int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, 
   p.rows = pl.rows;
   p.skv = s.Skv;
   p.hkv = s.Hkv;
+  p.kv_slabs = s.B * s.Hkv;
   p.nsplit = pl.nsplit;
   p.tiles_per_split = pl.tiles_per_split;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
@@ -308,7 +313,7 @@ int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, 
   const int smem = (3 * SM_TILE + SM_PTILE) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(fp32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 fwd)");
-  dim3 grid((pl.rows + SM_T - 1) / SM_T, s.B * s.Hkv, pl.nsplit);
+  dim3 grid((pl.rows + SM_T - 1) / SM_T, q_blocks_of(s) * s.B * s.Hkv, pl.nsplit);
   fp32_fwd_kernel<<<grid, 256, smem, st>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fp32_fwd_kernel launch");
@@ -329,6 +334,8 @@ int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, co
   p.rows = (s.Hq / s.Hkv) * s.Sq;
   p.skv = s.Skv;
   p.hkv = s.Hkv;
+  p.nblk = q_blocks_of(s);
+  p.kv_slabs = s.B * s.Hkv;
   p.scale = sm_scale;
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.dq_acc = dq_acc;

@@ -49,6 +49,7 @@ struct FwdParams {
   int rows;             // g * Sq
   int skv;              // K/V rows in the shard
   int hkv;              // KV heads (to find the batch index of a CTA)
+  int kv_slabs;         // B*Hkv: query slab z reads K/V slab z % kv_slabs (several query blocks per K/V)
   int nsplit;
   int tiles_per_split;
   const int32_t* kv_valid_len;
@@ -72,7 +73,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int mb = blockIdx.x, bh = blockIdx.y, split = blockIdx.z;
-  const int batch = bh / p.hkv;
+  const int kvs = bh % p.kv_slabs;      // K/V slab of this query slab
+  const int batch = kvs / p.hkv;
 
   // K/V tile range of this CTA, clipped to the valid prefix of the shard.
   int valid = p.skv;
@@ -233,13 +235,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int y = (tile0 + j) * 128;
           if (!mbar_wait(&bars[FB_K_EMPTY + s], ph ^ 1, abort_flag, p.status, FWD_CODE(2, FB_K_EMPTY))) break;
           mbar_arrive_expect_tx(&bars[FB_K_FULL + s], FWD_TILE_BYTES);
-          tma_load_3d(smem + FWD_OFF_K + s * FWD_TILE_BYTES, &tmK, &bars[FB_K_FULL + s], 0, y, bh);
-          tma_load_3d(smem + FWD_OFF_K + s * FWD_TILE_BYTES + FWD_HALF_BYTES, &tmK, &bars[FB_K_FULL + s], 64, y, bh);
+          tma_load_3d(smem + FWD_OFF_K + s * FWD_TILE_BYTES, &tmK, &bars[FB_K_FULL + s], 0, y, kvs);
+          tma_load_3d(smem + FWD_OFF_K + s * FWD_TILE_BYTES + FWD_HALF_BYTES, &tmK, &bars[FB_K_FULL + s], 64, y, kvs);
           k_issued = j + 1;
           if (!mbar_wait(&bars[FB_V_EMPTY + s], ph ^ 1, abort_flag, p.status, FWD_CODE(2, FB_V_EMPTY))) break;
           mbar_arrive_expect_tx(&bars[FB_V_FULL + s], FWD_TILE_BYTES);
-          tma_load_3d(smem + FWD_OFF_V + s * FWD_TILE_BYTES, &tmV, &bars[FB_V_FULL + s], 0, y, bh);
-          tma_load_3d(smem + FWD_OFF_V + s * FWD_TILE_BYTES + FWD_HALF_BYTES, &tmV, &bars[FB_V_FULL + s], 64, y, bh);
+          tma_load_3d(smem + FWD_OFF_V + s * FWD_TILE_BYTES, &tmV, &bars[FB_V_FULL + s], 0, y, kvs);
+          tma_load_3d(smem + FWD_OFF_V + s * FWD_TILE_BYTES + FWD_HALF_BYTES, &tmV, &bars[FB_V_FULL + s], 64, y, kvs);
           v_issued = j + 1;
         }
         // A CTA that is giving up must not leave while a copy into its shared memory is in flight.
@@ -361,7 +363,8 @@ FwdPlan plan_fwd(const lvx_shape& s) {
   p.rows = g * s.Sq;
   p.m_blocks = (p.rows + 255) / 256;
   p.kv_tiles = (s.Skv + 127) / 128;
-  const long base = long(p.m_blocks) * s.B * s.Hkv;
+  const int qb = q_blocks_of(s);
+  const long base = long(p.m_blocks) * s.B * s.Hkv * qb;
   const int sms = 148;  // plan for the full part; a fixed figure keeps the workspace size device-independent
   int best = 1;
   double best_cost = 1e300;
@@ -379,8 +382,8 @@ FwdPlan plan_fwd(const lvx_shape& s) {
   }
   p.nsplit = best;
   p.tiles_per_split = p.kv_tiles > 0 ? (p.kv_tiles + best - 1) / best : 0;
-  p.o_part_bytes = size_t(s.B) * s.Hkv * p.nsplit * p.rows * 128 * sizeof(float);
-  p.ml_part_bytes = size_t(s.B) * s.Hkv * p.nsplit * p.rows * 2 * sizeof(float);
+  p.o_part_bytes = size_t(qb) * s.B * s.Hkv * p.nsplit * p.rows * 128 * sizeof(float);
+  p.ml_part_bytes = size_t(qb) * s.B * s.Hkv * p.nsplit * p.rows * 2 * sizeof(float);
   p.ml_part_bytes = (p.ml_part_bytes + 255) & ~size_t(255);
   p.o_part_bytes = (p.o_part_bytes + 255) & ~size_t(255);
   return p;
@@ -395,7 +398,9 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   CUtensorMap tmQ, tmK, tmV;
   const int es = elt_size(s.dtype);
   const uint64_t row_bytes = uint64_t(128) * es;
-  int rc = make_tmap_3d(&tmQ, s.dtype, q, 128, pl.rows, uint64_t(s.B) * s.Hkv, row_bytes, row_bytes * pl.rows, 64, 128);
+  const int qb = q_blocks_of(s);
+  int rc = make_tmap_3d(&tmQ, s.dtype, q, 128, pl.rows, uint64_t(qb) * s.B * s.Hkv, row_bytes, row_bytes * pl.rows, 64,
+                        128);
   if (rc) return rc;
   // A shard with no K/V rows still launches (every CTA writes the empty partial); the maps then
   // describe one dummy row of Q so that encoding succeeds and nothing is ever loaded through them.
@@ -411,6 +416,7 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   p.rows = pl.rows;
   p.skv = s.Skv;
   p.hkv = s.Hkv;
+  p.kv_slabs = s.B * s.Hkv;
   p.nsplit = pl.nsplit;
   p.tiles_per_split = pl.tiles_per_split;
   p.kv_valid_len = kv_valid_len;
@@ -419,7 +425,7 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   p.ml_part = ml_part;
   p.status = status;
 
-  dim3 grid(pl.m_blocks, s.B * s.Hkv, pl.nsplit);
+  dim3 grid(pl.m_blocks, qb * s.B * s.Hkv, pl.nsplit);
   cudaError_t e;
   if (s.dtype == LVX_BF16) {
     e = cudaFuncSetAttribute(fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);

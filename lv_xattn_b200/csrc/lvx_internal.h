@@ -24,6 +24,7 @@ int* device_status_ptr();
 int validate_shape(const lvx_shape* s, const char* who);
 int validate_arch();
 
+inline int q_blocks_of(const lvx_shape& s) { return s.q_blocks > 1 ? s.q_blocks : 1; }
 inline int elt_size(int dtype) { return dtype == LVX_FP32 ? 4 : 2; }
 
 // Split-KV plan of the forward block; shared by the kernel launcher, the combine kernel and
@@ -56,6 +57,9 @@ int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& p, const void* q, c
 int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
                           const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                           float* dk_acc, float* dv_acc, int accumulate_dkdv, cudaStream_t st);
+int launch_fwd_merge_parts(const lvx_shape& s, const float* o_parts, const float* lse_parts, int count,
+                           size_t stride_o, size_t stride_lse, void* o_out, float* lse_out, cudaStream_t st);
+int launch_sum_cast(const float* parts, int count, size_t stride, void* out, int out_dtype, size_t n, cudaStream_t st);
 int launch_add_cast(const float* a, const float* b, void* out, int out_dtype, size_t n, cudaStream_t st);
 int launch_selftest(int mode, const void* a, const void* b, float* d_out, int* status, cudaStream_t st);
 

@@ -37,8 +37,9 @@ static bool plan_within(const lvx_shape& s, size_t cap, FwdPlan* out) {
   FwdPlan p = plan_fwd(s);
   for (;;) {
     p.tiles_per_split = p.kv_tiles > 0 ? (p.kv_tiles + p.nsplit - 1) / p.nsplit : 0;
-    p.o_part_bytes = (size_t(s.B) * s.Hkv * p.nsplit * p.rows * 128 * sizeof(float) + 255) & ~size_t(255);
-    p.ml_part_bytes = (size_t(s.B) * s.Hkv * p.nsplit * p.rows * 2 * sizeof(float) + 255) & ~size_t(255);
+    const size_t slabs = size_t(q_blocks_of(s)) * s.B * s.Hkv;
+    p.o_part_bytes = (slabs * p.nsplit * p.rows * 128 * sizeof(float) + 255) & ~size_t(255);
+    p.ml_part_bytes = (slabs * p.nsplit * p.rows * 2 * sizeof(float) + 255) & ~size_t(255);
     if (p.o_part_bytes + p.ml_part_bytes <= cap) {
       *out = p;
       return true;

@@ -78,13 +78,17 @@ def release_workspaces() -> None:
 
 
 def shape_of(q, k) -> _lib.LvxShape:
-    B, Hq, Sq, D = q.shape
+    """q is [B, Hq, Sq, D], or [n, B, Hq, Sq, D] for n query blocks that all attend the same K/V batch."""
+    nblk = 1
+    if q.dim() == 5:
+        nblk = q.shape[0]
+    B, Hq, Sq, D = q.shape[-4:]
     Bk, Hkv, Skv, Dk = k.shape
     if Bk != B or Dk != D:
         raise ValueError(f"q {tuple(q.shape)} and k {tuple(k.shape)} disagree on batch or head dimension")
     if Hq % Hkv:
         raise ValueError(f"{Hq} query heads are not a multiple of {Hkv} KV heads")
-    return _lib.make_shape(B, Hq, Hkv, Sq, Skv, D, q.dtype)
+    return _lib.make_shape(B, Hq, Hkv, Sq, Skv, D, q.dtype, nblk)
 
 
 class FwdPartials:
@@ -106,7 +110,7 @@ def fwd_partials(q, k, v, sm_scale, kv_valid_len=None) -> FwdPartials:
     shp = shape_of(q, k)
     fwd_bytes, _ = _lib.query_workspace(shp)
     ws = _workspace(q.device, fwd_bytes)
-    B = q.shape[0]
+    B = k.shape[0]
     if kv_valid_len is not None:
         if kv_valid_len.dtype != torch.int32 or kv_valid_len.numel() != B:
             raise ValueError("kv_valid_len must be an int32 tensor with one entry per batch element")
@@ -144,9 +148,9 @@ def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, fina
     final=True  -> O in q.dtype (the caller's result); final=False -> fp32 travelling form.
     lse is fp32 [B*Hq, Sq]."""
     part = fwd_partials(q, k, v, sm_scale, kv_valid_len)
-    B, Hq, Sq, D = q.shape
-    o_out = torch.empty(B, Hq, Sq, D, dtype=q.dtype if final else torch.float32, device=q.device)
-    lse_out = torch.empty(B * Hq, Sq, dtype=torch.float32, device=q.device)
+    Hq, Sq = q.shape[-3], q.shape[-2]
+    o_out = torch.empty(q.shape, dtype=q.dtype if final else torch.float32, device=q.device)
+    lse_out = torch.empty(q.numel() // (Hq * Sq * q.shape[-1]) * Hq, Sq, dtype=torch.float32, device=q.device)
     fwd_combine(part, o_in, lse_in, o_out, lse_out, final)
     return o_out, lse_out
 
@@ -156,7 +160,8 @@ def bwd_prep(o, do):
     _require_cuda(o, do)
     lib = _lib.load()
     o, do = _contig(o), _contig(do)
-    B, Hq, Sq, D = o.shape
+    Hq, Sq, D = o.shape[-3:]
+    B = o.numel() // (Hq * Sq * D)
     shp = _lib.make_shape(B, Hq, Hq, Sq, 0, D, o.dtype)
     delta = torch.empty(B * Hq, Sq, dtype=torch.float32, device=o.device)
     _lib.check(lib.lvx_bwd_prep(ctypes.byref(shp), _lib.ptr(o), _lib.ptr(do), _lib.ptr(delta), _lib.stream_ptr()),
@@ -184,6 +189,44 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
                                      _lib.ptr(dq_acc), _lib.ptr(dk_acc), _lib.ptr(dv_acc),
                                      1 if accumulate_dkdv else 0, None, 0, _lib.stream_ptr()), "lvx_bwd_block")
     _count()
+
+
+def fwd_merge_parts(o_parts, lse_parts, out_dtype, o_out=None, lse_out=None):
+    """Merge of finished partials of the same query block: o_parts fp32 [n, B, Hq, Sq, D], lse_parts fp32
+    [n, B*Hq, Sq] -> (o [B, Hq, Sq, D] in out_dtype, lse [B*Hq, Sq])."""
+    _require_cuda(o_parts, lse_parts, o_out, lse_out)
+    lib = _lib.load()
+    if o_parts.dtype != torch.float32 or lse_parts.dtype != torch.float32:
+        raise ValueError("partials must be fp32")
+    o_parts, lse_parts = _contig(o_parts), _contig(lse_parts)
+    n, B, Hq, Sq, D = o_parts.shape
+    shp = _lib.make_shape(B, Hq, Hq, Sq, 0, D, out_dtype)
+    if o_out is None:
+        o_out = torch.empty(B, Hq, Sq, D, dtype=out_dtype, device=o_parts.device)
+    if lse_out is None:
+        lse_out = torch.empty(B * Hq, Sq, dtype=torch.float32, device=o_parts.device)
+    _lib.check(lib.lvx_fwd_merge_parts(ctypes.byref(shp), _lib.ptr(o_parts), _lib.ptr(lse_parts), n, B * Hq * Sq * D,
+                                       B * Hq * Sq, _lib.ptr(o_out), _lib.ptr(lse_out), _lib.stream_ptr()),
+               "lvx_fwd_merge_parts")
+    _count()
+    return o_out, lse_out
+
+
+def sum_cast(parts, out_dtype, out=None):
+    """cast(sum over the leading axis) of an fp32 tensor [n, ...]."""
+    _require_cuda(parts, out)
+    lib = _lib.load()
+    if parts.dtype != torch.float32:
+        raise ValueError("sum_cast takes an fp32 tensor")
+    parts = _contig(parts)
+    n = parts.shape[0]
+    inner = parts.numel() // n
+    if out is None:
+        out = torch.empty(parts.shape[1:], dtype=out_dtype, device=parts.device)
+    _lib.check(lib.lvx_sum_cast(_lib.ptr(parts), n, inner, _lib.ptr(out), _lib.dtype_code(out_dtype), inner,
+                                _lib.stream_ptr()), "lvx_sum_cast")
+    _count()
+    return out
 
 
 def add_cast(a, b, out_dtype, out=None):

@@ -12,6 +12,11 @@ class _Part:
 
 def fwd_partials(q, k, v, sm_scale, kv_valid_len=None):
     kvl = None if kv_valid_len is None else [int(x) for x in kv_valid_len]
+    if q.dim() == 5:      # [n, B, Hq, Sq, D]: every block against the same K/V
+        outs = [orc.attention_fwd(qb, k, v, sm_scale, kvl) for qb in q]
+        o = torch.stack([a for a, _ in outs])
+        lse = torch.stack([b.reshape(-1, q.shape[-2]) for _, b in outs])
+        return _Part(o, lse.reshape(-1, q.shape[-2]), q.dtype)
     o, lse = orc.attention_fwd(q, k, v, sm_scale, kvl)
     return _Part(o, lse.reshape(-1, q.shape[2]), q.dtype)
 
@@ -19,20 +24,29 @@ def fwd_partials(q, k, v, sm_scale, kv_valid_len=None):
 def fwd_combine(part, o_in, lse_in, o_out, lse_out, final):
     o, lse = part.o, part.lse
     if o_in is not None:
+        assert o.dim() == 4
         B, H, S, D = o.shape
         o, lse = orc.merge_partials(o_in, lse_in.view(B, H, S), o, lse.view(B, H, S))
         lse = lse.reshape(-1, S)
     assert o_out.dtype == (part.dtype if final else torch.float32)
-    o_out.copy_(o)
-    lse_out.copy_(lse)
+    o_out.copy_(o.reshape(o_out.shape))
+    lse_out.copy_(lse.reshape(lse_out.shape))
 
 
 def bwd_prep(o, do):
-    B, H, S, D = o.shape
-    return (o.float() * do.float()).sum(-1).reshape(B * H, S)
+    S = o.shape[-2]
+    return (o.float() * do.float()).sum(-1).reshape(-1, S)
 
 
 def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None):
+    if q.dim() == 5:      # n query blocks, one K/V pass: dK/dV sum over the blocks
+        n = q.shape[0]
+        rows = lse.numel() // n
+        for i in range(n):
+            bwd_block(q[i], do[i], lse.reshape(n, -1)[i].reshape(-1, q.shape[-2]),
+                      delta.reshape(n, -1)[i].reshape(-1, q.shape[-2]), k, v, sm_scale, dq_acc[i], dk_acc, dv_acc,
+                      accumulate_dkdv or i > 0, kv_valid_len)
+        return
     B, Hq, Sq, D = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
     g = Hq // Hkv
@@ -65,6 +79,27 @@ def add_cast(a, b, out_dtype, out=None):
         return r.to(out_dtype)
     out.copy_(r.view(out.shape))
     return out
+
+
+def fwd_merge_parts(o_parts, lse_parts, out_dtype, o_out=None, lse_out=None):
+    n, B, H, S, D = o_parts.shape
+    o, lse = o_parts[0], lse_parts[0].view(B, H, S)
+    for i in range(1, n):
+        o, lse = orc.merge_partials(o, lse, o_parts[i], lse_parts[i].view(B, H, S))
+    o, lse = o.to(out_dtype), lse.reshape(B * H, S)
+    if o_out is not None:
+        o_out.copy_(o)
+        lse_out.copy_(lse)
+        return o_out, lse_out
+    return o, lse
+
+
+def sum_cast(parts, out_dtype, out=None):
+    r = parts.sum(0).to(out_dtype)
+    if out is not None:
+        out.copy_(r)
+        return out
+    return r
 
 
 def release_workspaces():

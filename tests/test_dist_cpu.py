@@ -76,18 +76,22 @@ def _run(world, case):
         assert ret[r][0] == "ok", f"rank {r}: {ret[r]}"
 
 
+@pytest.mark.parametrize("schedule", ["gather", "ring"])
 @pytest.mark.parametrize("world", [1, 2, 3, 4])
-def test_step_loop_fp32(world):
-    _run(world, (1, 4, 2, 24 * world, 64 * world, torch.float32, None, {}))
+def test_step_loop_fp32(world, schedule):
+    if world == 1 and schedule == "ring":
+        pytest.skip("one rank has no schedule")
+    _run(world, (1, 4, 2, 24 * world, 64 * world, torch.float32, None, {"schedule": schedule}))
 
 
 def test_step_loop_bf16_gqa_key_padding():
     # per-sample valid lengths: one sample ends inside rank 1's shard, one has nothing beyond rank 0
     _run(4, (2, 4, 1, 32, 256, torch.bfloat16, [200, 40], {}))
+    _run(4, (2, 4, 1, 32, 256, torch.bfloat16, [200, 40], {"schedule": "ring"}))
 
 
 def test_step_loop_no_overlap():
-    _run(2, (1, 2, 2, 32, 128, torch.float32, None, {"no_overlap": True}))
+    _run(2, (1, 2, 2, 32, 128, torch.float32, None, {"no_overlap": True, "schedule": "ring"}))
 
 
 def _hf_worker(rank, world, port, ret):

@@ -1,0 +1,75 @@
+"""Several query blocks against one K/V shard in a single launch (the all-blocks-per-pass schedule), and the
+two reduce kernels that finish it, through the C ABI wrappers, against the CPU oracle."""
+import math
+
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+SCALE = 1.0 / math.sqrt(128.0)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float32, 1e-4)])
+def test_blocks_forward_backward(cuda_device, dtype, tol):
+    from lv_xattn_b200 import ops, _lib
+    n, B, Hq, Hkv, Sq, Skv = 3, 2, 4, 2, 96, 640
+    d = cuda_device
+    _, k, v, _ = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 50, dtype)
+    valid = [640, 333]
+    qs, dos, refs = [], [], []
+    for i in range(n):
+        q, _, _, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 51 + i, dtype)
+        qs.append(q)
+        dos.append(do)
+        refs.append(orc.attention_fwd_bwd(q, k, v, do, SCALE, valid))
+    q_all, do_all = torch.stack(qs).to(d), torch.stack(dos).to(d)
+    kd, vd = k.to(d), v.to(d)
+    kvl = torch.tensor(valid, dtype=torch.int32, device=d)
+    o, lse = ops.fwd_block(q_all, kd, vd, SCALE, kv_valid_len=kvl)
+    assert o.shape == q_all.shape and lse.shape == (n * B * Hq, Sq)
+    delta = ops.bwd_prep(o, do_all)
+    dq = torch.zeros(q_all.shape, dtype=torch.float32, device=d)
+    dk = torch.full(k.shape, float("nan"), dtype=torch.float32, device=d)
+    dv = torch.full(k.shape, float("nan"), dtype=torch.float32, device=d)
+    ops.bwd_block(q_all, do_all, lse, delta, kd, vd, SCALE, dq, dk, dv, False, kv_valid_len=kvl)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    lse = lse.cpu().view(n, B, Hq, Sq)
+    for i in range(n):
+        o_ref, lse_ref, dq_ref, _, _ = refs[i]
+        assert (o[i].float().cpu() - o_ref).abs().max() <= tol
+        assert (lse[i] - lse_ref).abs().max() <= min(tol, 1e-3)
+        assert (dq[i].cpu() - dq_ref).abs().max() <= tol
+    dk_ref = sum(r[3] for r in refs)
+    dv_ref = sum(r[4] for r in refs)
+    assert (dk.cpu() - dk_ref).abs().max() <= tol * 2
+    assert (dv.cpu() - dv_ref).abs().max() <= tol * 2
+
+
+def test_merge_parts_and_sum_cast(cuda_device):
+    from lv_xattn_b200 import ops
+    B, Hq, Hkv, Sq, Skv = 1, 4, 2, 64, 768
+    d = cuda_device
+    q, k, v, _ = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 60, torch.bfloat16)
+    o_ref, lse_ref = orc.attention_fwd(q, k, v, SCALE, [500])
+    parts_o, parts_l = [], []
+    for i, valid in enumerate([256, 244, 0]):            # three shards of 256 keys, the last one all padding
+        kvl = torch.tensor([valid], dtype=torch.int32, device=d)
+        o, l = ops.fwd_block(q.to(d), k[:, :, 256 * i:256 * (i + 1)].to(d), v[:, :, 256 * i:256 * (i + 1)].to(d), SCALE,
+                             kv_valid_len=kvl, final=False)
+        parts_o.append(o)
+        parts_l.append(l)
+    o, lse = ops.fwd_merge_parts(torch.stack(parts_o), torch.stack(parts_l), torch.bfloat16)
+    assert (o.float().cpu() - o_ref).abs().max() <= 2e-2
+    assert (lse.cpu().view(B, Hq, Sq) - lse_ref).abs().max() <= 1e-3
+    # all-empty merge stays (0, -inf)
+    z = torch.zeros(2, 1, 1, 4, 128, device=d)
+    ninf = torch.full((2, 1, 4), float("-inf"), device=d)
+    o0, l0 = ops.fwd_merge_parts(z, ninf, torch.float32)
+    assert torch.equal(o0.cpu(), torch.zeros(1, 1, 4, 128)) and torch.isinf(l0).all()
+    parts = torch.randn(5, 3, 7, 128, device=d)
+    s = ops.sum_cast(parts, torch.float32)
+    assert torch.allclose(s, parts.sum(0), atol=1e-5)
+    assert ops.sum_cast(parts, torch.bfloat16).dtype == torch.bfloat16

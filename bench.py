@@ -189,7 +189,10 @@ def main():
 
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = os.environ.get("LVX_NCCL_DEBUG", "WARN")   # keep NCCL's banner off stdout
+        if "LVX_NCCL_DEBUG" in os.environ:
+            os.environ["NCCL_DEBUG"] = os.environ["LVX_NCCL_DEBUG"]
+        else:
+            os.environ.pop("NCCL_DEBUG", None)      # any level prints NCCL's version banner on stdout
         lvx.initialize_distributed("nccl")
 
     B, Hq, Hkv, D, Sq, Skv, dts = cfg

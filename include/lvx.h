@@ -105,7 +105,8 @@ int lvx_bwd_prep(const lvx_shape* s, const void* o, const void* d_o, float* delt
  *   dq_acc[B,Hq,Sq,D]   (fp32) += dS K            (reduce-add; the caller zeroes it)
  *   dk_acc[B,Hkv,Skv,D] (fp32) (+)= dS^T Q        (summed over the query heads of the KV group)
  *   dv_acc[B,Hkv,Skv,D] (fp32) (+)= P^T dO
- * accumulate_dkdv == 0 overwrites dk_acc/dv_acc, != 0 adds to them.
+ * accumulate_dkdv: 0 overwrites the fp32 dk_acc/dv_acc, 1 adds to them, 2 treats dk_acc/dv_acc as
+ * tensors of shape.dtype and writes the finished gradients there (single-pass use).
  * Replaces _flash_attn_backward / _bwd_kernel, lv_xattn/flash_attn_kernels.py:904-1020 and
  * :364-819, and the per-step accumulation lv_xattn/attn.py:523-527. */
 int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const float* lse, const float* delta,

@@ -180,42 +180,34 @@ def send_recv_bwd_rescale_reqs(dq_send, dq_recv, comm_mode):
     return _exchange([dq_send], [dq_recv], comm_mode)
 
 
-def p2p_all_gather(local_tensors, gathered, comm_mode):
-    """gathered[i][s] <- rank s's local_tensors[i] for every rank s (the own slot is a local copy).
-    One batch of P2P sends/receives: every peer pair exchanges directly over NVSwitch, which moves the same
-    bytes as W-1 ring hops in one launch."""
+def all_gather_blocks(local_tensors, gathered, comm_mode):
+    """gathered[i][s] <- rank s's local_tensors[i] for every rank s; gathered[i] is a contiguous [W, ...]
+    tensor. One NCCL all-gather per tensor (every pair exchanges directly over NVSwitch; the bytes per GPU
+    equal W-1 ring hops of the same block)."""
+    if comm_mode == "nocomm":
+        for t, g in zip(local_tensors, gathered):
+            g[get_sequence_parallel_rank()].copy_(t)
+        return []
     group = get_sequence_parallel_group()
-    r, w = get_sequence_parallel_rank(), get_sequence_parallel_size()
-    ops_ = []
-    for s in range(w):
-        if s != r:
-            for g in gathered:
-                ops_.append(P2POp(op=irecv, tensor=g[s], peer=s, group=group))
-    for s in range(w):
-        if s != r:
-            for t in local_tensors:
-                ops_.append(P2POp(op=isend, tensor=t, peer=s, group=group))
+    works = []
     for t, g in zip(local_tensors, gathered):
-        g[r].copy_(t)
-    return [launch_async_handles(ops_, comm_mode)]
+        works.append(dist.all_gather_into_tensor(g.view(-1), t.contiguous().view(-1), group=group, async_op=True))
+    return [works]
 
 
-def p2p_all_to_all(pairs, comm_mode):
-    """For every (send, recv) pair of [W, ...] tensors: send[s] goes to rank s, recv[s] comes from rank s."""
+def all_to_all_blocks(pairs, comm_mode):
+    """For every (send, recv) pair of contiguous [W, ...] tensors: send[s] goes to rank s, recv[s] comes from
+    rank s (one NCCL all-to-all per pair)."""
+    if comm_mode == "nocomm":
+        r = get_sequence_parallel_rank()
+        for sd, rv in pairs:
+            rv[r].copy_(sd[r])
+        return []
     group = get_sequence_parallel_group()
-    r, w = get_sequence_parallel_rank(), get_sequence_parallel_size()
-    ops_ = []
-    for s in range(w):
-        if s != r:
-            for _, rv in pairs:
-                ops_.append(P2POp(op=irecv, tensor=rv[s], peer=s, group=group))
-    for s in range(w):
-        if s != r:
-            for sd, _ in pairs:
-                ops_.append(P2POp(op=isend, tensor=sd[s], peer=s, group=group))
+    works = []
     for sd, rv in pairs:
-        rv[r].copy_(sd[r])
-    return [launch_async_handles(ops_, comm_mode)]
+        works.append(dist.all_to_all_single(rv.view(-1), sd.view(-1), group=group, async_op=True))
+    return [works]
 
 
 def launch_async_handles(handles, comm_mode):

@@ -29,8 +29,8 @@ from .async_communication import (
     get_sequence_parallel_rank,
     get_sequence_parallel_size,
     get_slabs,
-    p2p_all_gather,
-    p2p_all_to_all,
+    all_gather_blocks,
+    all_to_all_blocks,
     reset_global_memory_buffer,
     send_recv_bwd_comp_reqs,
     send_recv_bwd_rescale_reqs,
@@ -122,7 +122,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
     if _schedule(schedule) == "gather":
         q_all = _carve(get_slabs("g_q", W * n_o * es, dev, 1)[0], 0, (W, B, Hq, Sq, D), dt)
-        wait_async_handles(p2p_all_gather([qc], [q_all], comm_mode))
+        wait_async_handles(all_gather_blocks([qc], [q_all], comm_mode))
         part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl)
         sbuf = get_slabs("g_acc_send", W * (n_o + n_l) * 4, dev, 1)[0]
         rbuf = get_slabs("g_acc_recv", W * (n_o + n_l) * 4, dev, 1)[0]
@@ -131,7 +131,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         o_recv = _carve(rbuf, 0, (W, B, Hq, Sq, D), torch.float32)
         l_recv = _carve(rbuf, W * n_o * 4, (W, B * Hq, Sq), torch.float32)
         ops.fwd_combine(part, None, None, o_parts, l_parts.view(W * B * Hq, Sq), False)
-        wait_async_handles(p2p_all_to_all([(o_parts, o_recv), (l_parts, l_recv)], comm_mode))
+        wait_async_handles(all_to_all_blocks([(o_parts, o_recv), (l_parts, l_recv)], comm_mode))
         ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
         return q, k, v, o, L
 
@@ -210,24 +210,30 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
 
     if W == 1 or comm_mode == "nocomm":
         dq_acc = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
+        dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         for t in range(W):
             dq_acc.zero_()
-            ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk_acc, dv_acc, False, kvl)
+            ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl)
         ops.add_cast(dq_acc, None, dt, out=dq)
+        return dq, dk, dv
     elif _schedule(schedule) == "gather":
         gbuf = get_slabs("g_bwd_in", W * (2 * n_q * es + 2 * n_r * 4), dev, 1)[0]
         q_all = _carve(gbuf, 0, (W, B, Hq, Sq, D), dt)
         do_all = _carve(gbuf, W * n_q * es, (W, B, Hq, Sq, D), dt)
         l_all = _carve(gbuf, 2 * W * n_q * es, (W, B * Hq, Sq), torch.float32)
         d_all = _carve(gbuf, 2 * W * n_q * es + W * n_r * 4, (W, B * Hq, Sq), torch.float32)
-        wait_async_handles(p2p_all_gather([qc, doc, Lc, delta], [q_all, do_all, l_all, d_all], comm_mode))
+        wait_async_handles(all_gather_blocks([qc, doc, Lc, delta], [q_all, do_all, l_all, d_all], comm_mode))
         dq_parts = _carve(get_slabs("g_dq_send", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
         dq_recv = _carve(get_slabs("g_dq_recv", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
         dq_parts.zero_()
+        dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         ops.bwd_block(q_all, do_all, l_all.view(W * B * Hq, Sq), d_all.view(W * B * Hq, Sq), kc, vc, sm_scale,
-                      dq_parts, dk_acc, dv_acc, False, kvl)
-        wait_async_handles(p2p_all_to_all([(dq_parts, dq_recv)], comm_mode))
+                      dq_parts, dk, dv, "final", kvl)       # one pass: dK/dV leave the kernel in their final dtype
+        wait_async_handles(all_to_all_blocks([(dq_parts, dq_recv)], comm_mode))
         ops.sum_cast(dq_recv, dt, out=dq)
+        return dq, dk, dv
     else:
         slab_bytes = 2 * n_q * es + 2 * n_r * 4
         in_bufs = get_slabs("bwd_in", slab_bytes, dev, 3)

@@ -78,9 +78,9 @@ struct BwdParams {
   float scale;         // sm_scale
   float scale_log2;    // sm_scale * log2(e)
   float* dq_acc;       // [slab][rows][128]
-  float* dk_acc;       // [slab][skv][128]
+  float* dk_acc;       // [slab][skv][128]  (fp32; 16-bit when accumulate == 2)
   float* dv_acc;
-  int accumulate;
+  int accumulate;      // 0 overwrite fp32, 1 add to fp32, 2 write the finished gradient in the input dtype
   int debug;           // development switches (LVX_BWD_DEBUG); 0 in normal use
   int* status;
 };
@@ -291,14 +291,26 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           uint32_t a[32];
           tmem_ld32(tmem_base + (which ? TM_DV : TM_DK) + lane_sel + cg * 32, a);
           tc_wait_ld();
-          if (ok_row) {
+          const float mul = which ? 1.f : p.scale;
+          if (ok_row && p.accumulate == 2) {
+            uint4* d16 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(which ? p.dv_acc : p.dk_acc) + off);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = __uint_as_float(a[8 * i + 2 * e]) * mul, hi = __uint_as_float(a[8 * i + 2 * e + 1]) * mul;
+                w[e] = IS_BF16 ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+              }
+              d16[i] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else if (ok_row) {
             float4* d4 = reinterpret_cast<float4*>((which ? p.dv_acc : p.dk_acc) + off);
-            const float mul = which ? 1.f : p.scale;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               float4 v = make_float4(__uint_as_float(a[4 * i]) * mul, __uint_as_float(a[4 * i + 1]) * mul,
                                      __uint_as_float(a[4 * i + 2]) * mul, __uint_as_float(a[4 * i + 3]) * mul);
-              if (p.accumulate) {
+              if (p.accumulate == 1) {
                 const float4 o = d4[i];
                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
               }
@@ -430,13 +442,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
       }
     }
-  } else if (!poisoned && !p.accumulate && warp < 8) {
+  } else if (!poisoned && p.accumulate != 1 && warp < 8) {
     // No valid K/V row in this tile: its gradients are zero.
     const int r = tid & 127;
     if (kv0 + r < p.skv) {
-      float* dst = (warp < 4 ? p.dk_acc : p.dv_acc) + (size_t(slab) * p.skv + kv0 + r) * 128;
+      const size_t off = (size_t(slab) * p.skv + kv0 + r) * 128;
+      float* base = warp < 4 ? p.dk_acc : p.dv_acc;
+      if (p.accumulate == 2) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + off);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) reinterpret_cast<float4*>(base + off)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
   }
 

@@ -281,15 +281,15 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
   for (int i = 0; i < 4; ++i) {
     const int row = kv0 + ty * 4 + i;
     if (row >= p.skv) continue;
-    if (!live && p.accumulate) continue;
+    if (!live && p.accumulate == 1) continue;
     float* dkp = p.dk_acc + (size_t(slab) * p.skv + row) * 128;
     float* dvp = p.dv_acc + (size_t(slab) * p.skv + row) * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const int d = tx + 16 * c;
       const float a = dk[i][c] * p.scale, b = dv[i][c];
-      dkp[d] = p.accumulate ? dkp[d] + a : a;
-      dvp[d] = p.accumulate ? dvp[d] + b : b;
+      dkp[d] = p.accumulate == 1 ? dkp[d] + a : a;     // fp32 is its own final dtype (mode 2 == overwrite)
+      dvp[d] = p.accumulate == 1 ? dvp[d] + b : b;
     }
   }
 }

@@ -171,14 +171,21 @@ def bwd_prep(o, do):
 
 
 def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None):
-    """dq_acc += dS K ; dk_acc, dv_acc (+)= dS^T Q, P^T dO  (all fp32 accumulators, updated in place)."""
+    """dq_acc += dS K ; dk_acc, dv_acc (+)= dS^T Q, P^T dO.
+
+    accumulate_dkdv: False -> overwrite the fp32 dk_acc/dv_acc; True -> add to them; "final" -> dk_acc/dv_acc
+    are tensors of q.dtype and receive the finished gradients (single-pass use, no later accumulation)."""
     _require_cuda(q, do, lse, delta, k, v, dq_acc, dk_acc, dv_acc, kv_valid_len)
     lib = _lib.load()
     q, do, k, v = _contig(q), _contig(do), _contig(k), _contig(v)
     shp = shape_of(q, k)
-    for t, name in ((lse, "lse"), (delta, "delta"), (dq_acc, "dq_acc"), (dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
+    final = accumulate_dkdv == "final"
+    for t, name in ((lse, "lse"), (delta, "delta"), (dq_acc, "dq_acc")):
         if t.dtype != torch.float32 or not t.is_contiguous():
             raise ValueError(f"{name} must be a contiguous fp32 tensor")
+    for t, name in ((dk_acc, "dk_acc"), (dv_acc, "dv_acc")):
+        if t.dtype != (q.dtype if final else torch.float32) or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous {'in the input dtype' if final else 'fp32'}")
     if dq_acc.numel() != q.numel() or dk_acc.numel() != k.numel() or dv_acc.numel() != v.numel():
         raise ValueError("accumulator sizes do not match q / k / v")
     if kv_valid_len is not None:
@@ -187,7 +194,8 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
         _lib.check(lib.lvx_bwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
                                      _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale),
                                      _lib.ptr(dq_acc), _lib.ptr(dk_acc), _lib.ptr(dv_acc),
-                                     1 if accumulate_dkdv else 0, None, 0, _lib.stream_ptr()), "lvx_bwd_block")
+                                     2 if final else (1 if accumulate_dkdv else 0), None, 0,
+                                     _lib.stream_ptr()), "lvx_bwd_block")
     _count()
 
 

@@ -42,10 +42,17 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
     if q.dim() == 5:      # n query blocks, one K/V pass: dK/dV sum over the blocks
         n = q.shape[0]
         rows = lse.numel() // n
+        dk32, dv32 = torch.zeros(k.shape), torch.zeros(v.shape)
         for i in range(n):
             bwd_block(q[i], do[i], lse.reshape(n, -1)[i].reshape(-1, q.shape[-2]),
-                      delta.reshape(n, -1)[i].reshape(-1, q.shape[-2]), k, v, sm_scale, dq_acc[i], dk_acc, dv_acc,
-                      accumulate_dkdv or i > 0, kv_valid_len)
+                      delta.reshape(n, -1)[i].reshape(-1, q.shape[-2]), k, v, sm_scale, dq_acc[i], dk32, dv32,
+                      True, kv_valid_len)
+        if accumulate_dkdv is True:
+            dk_acc += dk32
+            dv_acc += dv32
+        else:
+            dk_acc.copy_(dk32)
+            dv_acc.copy_(dv32)
         return
     B, Hq, Sq, D = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
@@ -65,7 +72,7 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
     dk = torch.matmul(ds.transpose(2, 3), qf)
     dk = dk.view(B, Hkv, g, Skv, D).sum(2)
     dv = dv.view(B, Hkv, g, Skv, D).sum(2)
-    if accumulate_dkdv:
+    if accumulate_dkdv is True:
         dk_acc += dk
         dv_acc += dv
     else:

@@ -137,7 +137,7 @@ def run_reference(args, cfg):
     threads = os.cpu_count() or 1
     vals = []
     for i in range(args.warmup + args.steps):
-        tf, dt, desc = cpu_attention_sample(cfg, threads, 1)
+        tf, dt, desc = cpu_attention_sample(cfg, threads, 4)
         if i >= args.warmup:
             vals.append((tf, dt))
     tf = sum(v[0] for v in vals) / len(vals)
@@ -297,7 +297,7 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        tf, dt, desc = cpu_attention_sample(cfg, threads, 4)
+        tf, dt, desc = cpu_attention_sample(cfg, threads, 16)
         cpu = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc, "seconds": dt}
 
     if rank == 0:

@@ -11,8 +11,9 @@ the N ranks (rank r takes the r-th slice, reference test.py:164-178). Inputs are
 A step = one forward + one backward of the layer through lv_xattn_b200._attn_forward/_attn_backward.
   value   whole-job algorithmic TFLOP/s (3.5 * 4*Hq*D*Sq*Skv per step over all ranks), inputs resident in HBM,
           device time from CUDA events summed over the K steps, max over ranks
-  e2e     the same through the autograd entry point with HOST (pinned) inputs: H2D of q,k,v,dO and D2H of
-          o,dq,dk,dv inside the timed region
+  e2e     the same through lv_xattn_b200.HostStreamedAttention.step with HOST (pinned) inputs and outputs:
+          H2D of q,k,v,dO and D2H of o,dq,dk,dv inside the timed region (at N=1 the K/V shard is streamed in
+          chunks so that the kernels overlap the copies)
   roofline  the backward block kernel: algorithmic FLOPs of its launches / its event-timed duration, against
           the measured bf16 tensor peak
   cpu_baseline  the CPU oracle (reference test.py:129-156 math) timed on the host cores on a bounded sample
@@ -274,17 +275,10 @@ def main():
         ho = torch.empty_like(hq)
         hdq, hdk, hdv = torch.empty_like(hq), torch.empty_like(hk), torch.empty_like(hv)
 
+        streamer = lvx.HostStreamedAttention(dev, chunks=4)
+
         def step_e2e():
-            dq_, dk_, dv_, dd = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
-            dq_.requires_grad_(True)
-            dk_.requires_grad_(True)
-            dv_.requires_grad_(True)
-            o = lvx.attention(dq_, dk_, dv_, False, scale)
-            o.backward(dd)
-            ho.copy_(o.detach(), non_blocking=True)
-            hdq.copy_(dq_.grad, non_blocking=True)
-            hdk.copy_(dk_.grad, non_blocking=True)
-            hdv.copy_(dv_.grad, non_blocking=True)
+            streamer.step(hq, hk, hv, hdo, scale, ho, hdq, hdk, hdv)
 
         e_steps = max(1, min(args.steps, 5))
         e_ms, _ = timed(step_e2e, e_steps, 1)

@@ -27,3 +27,4 @@ from .hf_patch import (  # noqa: F401,E402
     patch_self_attention_forward,
     set_global_cross_attention_states,
 )
+from .host_io import HostStreamedAttention  # noqa: F401,E402

@@ -19,6 +19,8 @@
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
 #include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 namespace lvx {
 
@@ -56,8 +58,17 @@ struct FwdParams {
   float scale_log2;     // sm_scale * log2(e)
   float* o_part;        // [B*Hkv][nsplit][rows][128]
   float* ml_part;       // [B*Hkv][nsplit][rows][2]
+  int debug;
   int* status;
 };
+
+// Development aid (LVX_FWD_DEBUG=1): cycle stamps of CTA (0,0,0), K/V tiles 4..11, 8 slots per tile and role.
+__device__ long long g_fwd_ts[3 * 8 * 8];
+#define FWD_TS(role, slot)                                                                              \
+  do {                                                                                                  \
+    if (p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && j >= 4 && j < 12) \
+      g_fwd_ts[((role) * 8 + (j - 4)) * 8 + (slot)] = clock64();                                        \
+  } while (0)
 
 #define FWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x100 | ((role) << 5) | (bar))
 
@@ -130,12 +141,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           break;
         }
         tc_fence_after();
+        if ((warp & 3) == 0) FWD_TS(wg, 0);
         uint32_t s[4][32];
         tmem_ld32(tS + 0, s[0]);
         tmem_ld32(tS + 32, s[1]);
         tmem_ld32(tS + 64, s[2]);
         tmem_ld32(tS + 96, s[3]);
         tc_wait_ld();
+        if ((warp & 3) == 0) FWD_TS(wg, 1);
         if (j == n - 1 && last_cols < 128) {
 #pragma unroll
           for (int q = 0; q < 4; ++q)
@@ -172,6 +185,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tmem_st32(tO + q * 32, o);
           }
         }
+        if ((warp & 3) == 0) FWD_TS(wg, 2);
         const float moff = (m == -INFINITY) ? 0.f : m;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
@@ -191,10 +205,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           tmem_st32(tS + h * 32, pk);
         }
         l += sum0 + sum1;
+        if ((warp & 3) == 0) FWD_TS(wg, 3);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[FB_P_FULL + wg]);
+        if ((warp & 3) == 0) FWD_TS(wg, 4);
       }
       // ------------------------------- epilogue -------------------------------
       const int row = mb * 256 + wg * 128 + row_in_tile;
@@ -300,17 +316,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int s1 = (j + 1) % FWD_NS;
           const uint32_t ph1 = ((j + 1) / FWD_NS) & 1;
           for (int i = 0; i < 2 && ok; ++i) {
+            FWD_TS(2, i * 4 + 0);
             ok = mbar_wait(&bars[FB_P_FULL + i], j & 1, abort_flag, p.status, FWD_CODE(3, FB_P_FULL));
+            FWD_TS(2, i * 4 + 1);
             if (ok && i == 0) ok = mbar_wait(&bars[FB_V_FULL + s], ph, abort_flag, p.status, FWD_CODE(3, FB_V_FULL));
             if (!ok) break;
             tc_fence_after();
             issue_pv(i, s, j == 0);
+            FWD_TS(2, i * 4 + 2);
             if (i == 1) tc_commit(&bars[FB_V_EMPTY + s]);
             if (j + 1 < n) {
               if (i == 0) ok = mbar_wait(&bars[FB_K_FULL + s1], ph1, abort_flag, p.status, FWD_CODE(3, FB_K_FULL));
               if (!ok) break;
               tc_fence_after();
               issue_qk(i, s1);
+              FWD_TS(2, i * 4 + 3);
               tc_commit(&bars[FB_S_FULL + i]);
               if (i == 1) tc_commit(&bars[FB_K_EMPTY + s1]);
             } else {
@@ -424,6 +444,7 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   p.o_part = o_part;
   p.ml_part = ml_part;
   p.status = status;
+  p.debug = getenv("LVX_FWD_DEBUG") ? 1 : 0;
 
   dim3 grid(pl.m_blocks, qb * s.B * s.Hkv, pl.nsplit);
   cudaError_t e;
@@ -438,6 +459,18 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_kernel launch");
+  if (p.debug) {
+    static long long ts[3 * 8 * 8];
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(ts, g_fwd_ts, sizeof(ts));
+    const char* names[3] = {"softmax0", "softmax1", "mma"};
+    for (int r = 0; r < 3; ++r)
+      for (int j = 0; j < 8; ++j) {
+        fprintf(stderr, "%s tile %d:", names[r], j + 4);
+        for (int k2 = 0; k2 < 8; ++k2) fprintf(stderr, " %lld", ts[(r * 8 + j) * 8 + k2] ? ts[(r * 8 + j) * 8 + k2] - ts[0] : -1);
+        fprintf(stderr, "\n");
+      }
+  }
   return LVX_OK;
 }
 

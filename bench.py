@@ -272,8 +272,8 @@ def main():
     e2e = None
     if not args.no_e2e:
         hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
-        ho = torch.empty_like(hq)
-        hdq, hdk, hdv = torch.empty_like(hq), torch.empty_like(hk), torch.empty_like(hv)
+        ho, hdq = torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory()
+        hdk, hdv = torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()
 
         streamer = lvx.HostStreamedAttention(dev, chunks=4)
 

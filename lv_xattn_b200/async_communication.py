@@ -124,18 +124,19 @@ def get_slabs(kind: str, nbytes: int, device, count: int = 2):
     return bufs
 
 
-def maybe_get_set_global_memory_buffer(q, o_acc_nbytes: int):
-    """Forward pools: two Q slabs and two [O | lse] accumulator slabs sized for this call."""
-    qs = get_slabs("fwd_q", q.numel() * q.element_size(), q.device)
-    accs = get_slabs("fwd_acc", o_acc_nbytes, q.device)
-    return qs, accs
+def maybe_get_set_global_memory_buffer(q, acc_nbytes: int):
+    """Forward ring pools: two Q slabs, two outgoing and two incoming [O | lse] accumulator slabs
+    (the reference keeps 2x{Q, M, L, O}, lv_xattn/async_communication.py:95-108)."""
+    n = q.numel() * q.element_size()
+    return (get_slabs("fwd_q", n, q.device, 2), get_slabs("fwd_acc_send", acc_nbytes, q.device, 2),
+            get_slabs("fwd_acc_recv", acc_nbytes, q.device, 2))
 
 
 def maybe_get_set_global_memory_buffer_bwd(slab_nbytes: int, dq_nbytes: int, device):
-    """Backward pools: two [Q | dO | lse | delta] slabs and two fp32 dQ slabs."""
-    slabs = get_slabs("bwd_in", slab_nbytes, device)
-    dqs = get_slabs("bwd_dq", dq_nbytes, device, count=3)
-    return slabs, dqs
+    """Backward ring pools: three [Q | dO | lse | delta] slabs, two outgoing and two incoming fp32 dQ slabs
+    (reference: lv_xattn/async_communication.py:110-133)."""
+    return (get_slabs("bwd_in", slab_nbytes, device, 3), get_slabs("bwd_dq_send", dq_nbytes, device, 2),
+            get_slabs("bwd_dq_recv", dq_nbytes, device, 2))
 
 
 def reset_global_memory_buffer():

@@ -29,6 +29,8 @@ from .async_communication import (
     get_sequence_parallel_rank,
     get_sequence_parallel_size,
     get_slabs,
+    maybe_get_set_global_memory_buffer,
+    maybe_get_set_global_memory_buffer_bwd,
     all_gather_blocks,
     all_to_all_blocks,
     reset_global_memory_buffer,
@@ -136,9 +138,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         return q, k, v, o, L
 
     acc_bytes = n_o * 4 + n_l * 4
-    q_bufs = get_slabs("fwd_q", n_o * es, dev, 2)
-    send_bufs = get_slabs("fwd_acc_send", acc_bytes, dev, 2)
-    recv_bufs = get_slabs("fwd_acc_recv", acc_bytes, dev, 2)
+    q_bufs, send_bufs, recv_bufs = maybe_get_set_global_memory_buffer(qc, acc_bytes)
 
     def acc_views(buf, final):
         odt = dt if final else torch.float32
@@ -236,10 +236,8 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         return dq, dk, dv
     else:
         slab_bytes = 2 * n_q * es + 2 * n_r * 4
-        in_bufs = get_slabs("bwd_in", slab_bytes, dev, 3)
+        in_bufs, send_bufs, recv_bufs = maybe_get_set_global_memory_buffer_bwd(slab_bytes, n_q * 4, dev)
         dq_delta = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
-        send_bufs = get_slabs("bwd_dq_send", n_q * 4, dev, 2)
-        recv_bufs = get_slabs("bwd_dq_recv", n_q * 4, dev, 2)
 
         def slab_views(buf):
             return (_carve(buf, 0, (B, Hq, Sq, D), dt), _carve(buf, n_q * es, (B, Hq, Sq, D), dt),

@@ -16,18 +16,28 @@
 // 70 cycles or more whatever its N, so 64-wide query tiles (which would leave TMEM room for double
 // buffering) run the pipe at half efficiency. With 128-wide tiles the 512 TMEM columns are exactly
 //     dK [0,128)  dV [128,256)  X [256,384)  Y [384,512)
-//     X: S^T (fp32)  ->  P^T | dS^T (16-bit, 64 columns each)      Y: dP^T (fp32)  ->  dQ^T (fp32)
-// so a tile's phases are serial (MMA: S^T,dP^T | all warps: P^T,dS^T | MMA: dQ^T,dV,dK,S^T',dP^T' with the
-// dQ^T drain and its reduce-adds overlapping the last four), and 16 compute warps keep the exposed
-// elementwise phase short.
+//     X: S^T (fp32)  ->  P^T (16-bit, 64 columns)                  Y: dP^T (fp32)  ->  dQ^T (fp32)
+// dS^T lives in shared memory only: it is the B operand of dQ^T (read MN-major) and the A operand of dK (the
+// same bytes read K-major), which frees X as soon as dV has consumed P^T.
+// so the MMA work of a tile is issued as one run (dQ^T, dV, dK of tile j, then S^T, dP^T of tile j+1). What keeps
+// the tensor pipe fed is that nothing else sits on that critical path:
+//   * the P^T half of the elementwise work (the exp) starts as soon as S^T of the next tile is complete, i.e.
+//     while dP^T is still in the pipe; only the dS^T half waits for dP^T;
+//   * the dQ^T tile is taken out of TMEM and reduce-added by four dedicated drain warps. The reduce traffic
+//     (64 KB per tile) moves at ~21 B/clk/SM, about as long as the whole MMA run, so it must not be issued by
+//     the warps that produce P^T/dS^T.
 //
-// CTA anatomy (576 threads)
+// CTA anatomy (832 threads, 72 registers each)
 //   warps 0-15  compute: warp w works on K/V rows 32*(w%4).. (its TMEM lane quarter) and query columns
-//               32*(w/4)..; the same warps drain dQ^T (rows = head dim) and write dK/dV at the end
-//   warp  16    TMA producer: K,V once; Q,dO tiles through a 2-stage ring
-//   warp  17    tcgen05.mma issuer; owns the TMEM allocation
+//               32*(w/4)..; they also write dK/dV at the end
+//   warps 16-23 dQ drain: warp w takes lane quarter w%4 of dQ^T (rows = head dim) and 64 of its query columns,
+//               all loaded at once so that Y is free again right away (a warp sustains about one reduce-add
+//               per 60 cycles, so eight warps are needed to keep up with one tile per ~4,000 cycles)
+//   warp  24    TMA producer: K,V once; Q,dO tiles through a 2-stage ring
+//   warp  25    tcgen05.mma issuer; owns the TMEM allocation
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
+#include <cuda_fp16.h>
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -45,7 +55,10 @@ constexpr int BWD_OFF_STAT = BWD_OFF_DS + BWD_TILE;              // [2][lse2 128
 constexpr int BWD_OFF_BAR = BWD_OFF_STAT + 2 * 256 * 4;
 constexpr int BWD_SMEM = BWD_OFF_BAR + 256;
 constexpr int BWD_COMPUTE_WARPS = 16;
-constexpr int BWD_THREADS = (BWD_COMPUTE_WARPS + 2) * 32;
+constexpr int BWD_DRAIN_WARPS = 8;
+constexpr int BWD_WARP_TMA = BWD_COMPUTE_WARPS + BWD_DRAIN_WARPS;
+constexpr int BWD_WARP_MMA = BWD_WARP_TMA + 1;
+constexpr int BWD_THREADS = (BWD_WARP_MMA + 1) * 32;
 static_assert(BWD_SMEM <= 232448, "shared memory budget");
 
 constexpr uint32_t TM_DK = 0, TM_DV = 128, TM_X = 256, TM_Y = 384;
@@ -56,7 +69,9 @@ enum {
   BB_Q_EMPTY = BB_Q_FULL + BWD_NSQ,    // x2
   BB_S_FULL = BB_Q_EMPTY + BWD_NSQ,
   BB_DP_FULL,
-  BB_XY_LOADED,
+  BB_X_LOADED,
+  BB_P_FULL,
+  BB_DS_FREE,                          // dQ^T and dK of a tile have both finished reading dS^T
   BB_PDS_FULL,
   BB_DQ_FULL,
   BB_DQ_FREE,
@@ -96,6 +111,12 @@ __device__ long long g_bwd_ts[2 * 8 * 16];
 #define BWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x200 | ((role) << 5) | (bar))
 
 template <bool IS_BF16>
+__device__ __forceinline__ float2 unpack16x2(uint32_t v) {
+  if (IS_BF16) return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&v));
+}
+
+template <bool IS_BF16>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
            const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
@@ -129,17 +150,19 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
     mbar_init(&bars[BB_S_FULL], 1);
     mbar_init(&bars[BB_DP_FULL], 1);
-    mbar_init(&bars[BB_XY_LOADED], BWD_COMPUTE_WARPS);
+    mbar_init(&bars[BB_X_LOADED], BWD_COMPUTE_WARPS);
+    mbar_init(&bars[BB_P_FULL], BWD_COMPUTE_WARPS);
+    mbar_init(&bars[BB_DS_FREE], 1);
     mbar_init(&bars[BB_PDS_FULL], BWD_COMPUTE_WARPS);
     mbar_init(&bars[BB_DQ_FULL], 1);
-    mbar_init(&bars[BB_DQ_FREE], BWD_COMPUTE_WARPS);
+    mbar_init(&bars[BB_DQ_FREE], BWD_DRAIN_WARPS);
     mbar_init(&bars[BB_ACC_DONE], 1);
     mbar_init(&bars[BB_DRAIN], 1);
     for (int b = 0; b < 2; ++b) mbar_init(&bars[BB_STAT_FULL + b], 8);   // warps 0-7 publish
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 17) {
+  if (warp == BWD_WARP_MMA) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -190,49 +213,82 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         float stat_after = 0.f;
         if (j + 2 < ntot) stat_after = fetch_stat(j + 2);
         if (warp == 0) BWD_TS(0, 0);
-        if (!mbar_wait(&bars[BB_S_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL)) ||
-            !mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL))) {
+        // ---------------- P^T half: needs S^T only ----------------
+        if (!mbar_wait(&bars[BB_S_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL))) {
           alive = false;
           break;
         }
         tc_fence_after();
         if (warp == 0) BWD_TS(0, 1);
-        uint32_t s[32], dp[32];
+        uint32_t s[32];
         tmem_ld32(tX + cg * 32, s);
-        tmem_ld32(tY + cg * 32, dp);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_XY_LOADED]);
+        if (lane == 0) mbar_arrive(&bars[BB_X_LOADED]);
         if (!mbar_wait(&bars[BB_STAT_FULL + (j & 1)], (j >> 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_STAT_FULL))) {
           alive = false;
           break;
         }
-        if (warp == 0) BWD_TS(0, 2);
         const float4* sl = reinterpret_cast<const float4*>(s_stat + (j & 1) * 256 + cg * 32);
         const float4* sd = reinterpret_cast<const float4*>(s_stat + (j & 1) * 256 + 128 + cg * 32);
-        uint32_t pk[16], dsk[16];
+        uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const float4 l2 = sl[i];
-          const float4 dl = sd[i];
           float p0 = ex2f(fmaf(__uint_as_float(s[4 * i]), c, -l2.x));
           float p1 = ex2f(fmaf(__uint_as_float(s[4 * i + 1]), c, -l2.y));
           float p2 = ex2f(fmaf(__uint_as_float(s[4 * i + 2]), c, -l2.z));
           float p3 = ex2f(fmaf(__uint_as_float(s[4 * i + 3]), c, -l2.w));
           if (tile_partial && !row_valid) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
-          const float d0 = p0 * (__uint_as_float(dp[4 * i]) - dl.x);
-          const float d1 = p1 * (__uint_as_float(dp[4 * i + 1]) - dl.y);
-          const float d2 = p2 * (__uint_as_float(dp[4 * i + 2]) - dl.z);
-          const float d3 = p3 * (__uint_as_float(dp[4 * i + 3]) - dl.w);
           pk[2 * i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
           pk[2 * i + 1] = IS_BF16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
-          dsk[2 * i] = IS_BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
-          dsk[2 * i + 1] = IS_BF16 ? pack_bf16x2(d2, d3) : pack_f16x2(d2, d3);
         }
+        if (warp == 0) BWD_TS(0, 2);
+        // P^T overwrites S^T in X: wait until every warp has taken its S^T columns out.
+        if (!mbar_wait(&bars[BB_X_LOADED], j & 1, abort_flag, p.status, BWD_CODE(0, BB_X_LOADED))) {
+          alive = false;
+          break;
+        }
+        tmem_st16(tX + cg * 16, pk);
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[BB_P_FULL]);      // dV of this tile may start
+        // ---------------- dS^T half: needs dP^T ----------------
+        if (!mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL))) {
+          alive = false;
+          break;
+        }
+        tc_fence_after();
         if (warp == 0) BWD_TS(0, 3);
-        // dS^T row -> shared memory: two 64-column halves, each 128-byte swizzled (chunk ^ row%8).
-        // The buffer is free: dQ^T of the previous tile was complete before this warp drained it.
+        uint32_t dsk[16];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t dp[16];
+          tmem_ld16(tY + cg * 32 + h * 16, dp);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            // P is taken back from its packed 16-bit form (the value the dV product uses), which keeps only
+            // 16 registers alive across the wait for dP^T
+            const float4 dl = sd[h * 4 + i];
+            const float2 pa = unpack16x2<IS_BF16>(pk[h * 8 + 2 * i]), pb = unpack16x2<IS_BF16>(pk[h * 8 + 2 * i + 1]);
+            const float d0 = pa.x * (__uint_as_float(dp[4 * i]) - dl.x);
+            const float d1 = pa.y * (__uint_as_float(dp[4 * i + 1]) - dl.y);
+            const float d2 = pb.x * (__uint_as_float(dp[4 * i + 2]) - dl.z);
+            const float d3 = pb.y * (__uint_as_float(dp[4 * i + 3]) - dl.w);
+            dsk[h * 8 + 2 * i] = IS_BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
+            dsk[h * 8 + 2 * i + 1] = IS_BF16 ? pack_bf16x2(d2, d3) : pack_f16x2(d2, d3);
+          }
+        }
+        tc_fence_before();
+        // dS^T row -> shared memory: two 64-column halves, each 128-byte swizzled (chunk ^ row%8). The
+        // previous tile's dQ^T and dK products must have finished reading the buffer.
+        if (j > 0 && !mbar_wait(&bars[BB_DS_FREE], (j - 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_DS_FREE))) {
+          alive = false;
+          break;
+        }
         {
           uint8_t* rowp = smem + BWD_OFF_DS + (cg >> 1) * BWD_HALF + r * 128;
 #pragma unroll
@@ -241,44 +297,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             *reinterpret_cast<uint4*>(rowp + ((((cg & 1) * 4 + ch) ^ (r & 7)) << 4)) = v;
           }
         }
-        // P^T and dS^T overwrite S^T in X: wait until every warp has taken its S^T columns out.
-        if (!mbar_wait(&bars[BB_XY_LOADED], j & 1, abort_flag, p.status, BWD_CODE(0, BB_XY_LOADED))) {
-          alive = false;
-          break;
-        }
-        tmem_st16(tX + cg * 16, pk);
-        tmem_st16(tX + 64 + cg * 16, dsk);
-        tc_wait_st();
-        tc_fence_before();
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[BB_PDS_FULL]);
         if (warp == 0) BWD_TS(0, 4);
         if (j + 1 < ntot) put_stat(j + 1, stat_next);
         stat_next = stat_after;
-        // ---- drain dQ^T of this tile: Y holds [head dim (lanes)][query (columns)] ----
-        if (!mbar_wait(&bars[BB_DQ_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DQ_FULL))) {
-          alive = false;
-          break;
-        }
-        tc_fence_after();
-        if (warp == 0) BWD_TS(0, 5);
-        uint32_t dq[32];
-        tmem_ld32(tY + cg * 32, dq);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);
-        if (warp == 0) BWD_TS(0, 6);
-        if (!(p.debug & 1)) {
-          const int q0 = tile_row0(j) + cg * 32;
-          const int ncols = min(32, p.rows - q0);
-          float* dst = p.dq_acc + (size_t(tile_slab(j)) * p.rows + q0) * 128 + r;
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i < ncols) atomicAdd(dst + i * 128, __uint_as_float(dq[i]) * p.scale);
-        }
-        if (warp == 0) BWD_TS(0, 7);
       }
       // ------------------------------- dK / dV epilogue -------------------------------
       if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], 0, abort_flag, p.status, BWD_CODE(0, BB_ACC_DONE));
@@ -319,7 +343,35 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           }
         }
       }
-    } else if (warp == 16) {
+    } else if (warp < BWD_WARP_TMA) {
+      // =========================== dQ drain warps ===========================
+      const int quarter = warp & 3;
+      const int ch = (warp - BWD_COMPUTE_WARPS) >> 2;      // which 64 query columns
+      const int d = quarter * 32 + lane;                    // head-dim index = TMEM lane of dQ^T
+      const uint32_t tY = tmem_base + TM_Y + (static_cast<uint32_t>(quarter * 32) << 16) + ch * 64;
+      for (int j = 0; j < ntot; ++j) {
+        if (!mbar_wait(&bars[BB_DQ_FULL], j & 1, abort_flag, p.status, BWD_CODE(1, BB_DQ_FULL))) break;
+        tc_fence_after();
+        if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 5);
+        uint32_t v[2][32];
+        tmem_ld32(tY, v[0]);
+        tmem_ld32(tY + 32, v[1]);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);     // Y is free for the next tile's dP^T
+        if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 6);
+        if (!(p.debug & 1)) {
+          const int row0 = (j % nq) * 128 + ch * 64;
+          const int ncols = min(64, p.rows - row0);
+          float* dst = p.dq_acc + (size_t(slab + (j / nq) * p.kv_slabs) * p.rows + row0) * 128 + d;
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if (i < ncols) atomicAdd(dst + size_t(i) * 128, __uint_as_float(v[i >> 5][i & 31]) * p.scale);
+        }
+        if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 7);
+      }
+    } else if (warp == BWD_WARP_TMA) {
       // =========================== TMA producer ===========================
       if (lane == 0) {
         tma_prefetch_desc(&tmQ);
@@ -382,6 +434,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             umma_ts_f16(d_tmem, a_tmem + kk * 8, umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_ACC,
                         (!first) || kk > 0);
         };
+        // dK[128 kv, 128 d] += dS^T[128 kv, 128 q] * Q[128 q, 128 d]: A is the dS^T tile in shared memory read
+        // K-major (rows kv, 64-column halves), B is Q read MN-major (rows are q)
+        auto issue_dk = [&](uint32_t b_smem, bool first) {
+          const uint32_t a_lo = umma_desc_lo(sDS, 16), b_lo = umma_desc_lo(b_smem, BWD_HALF);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_ss_f16(tmem_base + TM_DK, umma_desc_join(a_lo + (((kk >> 2) * BWD_HALF + (kk & 3) * 32) >> 4), HI),
+                        umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_ACC, (!first) || kk > 0);
+        };
         // D[128 d, 128 q] = K^T[128 d, 128 kv] * dS^T[128 kv, 128 q]  (both MN-major: rows are kv)
         const uint32_t kT_lo = umma_desc_lo(sK, BWD_HALF), ds_lo = umma_desc_lo(sDS, BWD_HALF);
         auto issue_dq = [&]() {
@@ -404,26 +465,34 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int s = j % BWD_NSQ;
           const uint32_t sQ = sQ0 + s * 2 * BWD_TILE, sDO = sQ + BWD_TILE;
           BWD_TS(1, 0);
-          ok = mbar_wait(&bars[BB_PDS_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL));
+          // dV needs P^T only, which is published before the dS^T half of the elementwise work; once dV has
+          // read X, S^T of the next tile can go there, i.e. while the warps are still producing dS^T
+          ok = mbar_wait(&bars[BB_P_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_P_FULL));
           if (!ok) break;
           tc_fence_after();
-          BWD_TS(1, 1);
-          issue_dq();                                   // Y: every warp took dP^T out before publishing P^T/dS^T
-          tc_commit(&bars[BB_DQ_FULL]);
-          BWD_TS(1, 2);
           issue_acc(tmem_base + TM_DV, tmem_base + TM_X, sDO, j == 0);
-          issue_acc(tmem_base + TM_DK, tmem_base + TM_X + 64, sQ, j == 0);
-          tc_commit(&bars[BB_Q_EMPTY + s]);
-          BWD_TS(1, 3);
+          BWD_TS(1, 1);
+          const int s1 = (j + 1) % BWD_NSQ;
+          const uint32_t sQ1 = sQ0 + s1 * 2 * BWD_TILE;
           if (j + 1 < ntot) {
-            const int s1 = (j + 1) % BWD_NSQ;
-            const uint32_t sQ1 = sQ0 + s1 * 2 * BWD_TILE;
             ok = mbar_wait(&bars[BB_Q_FULL + s1], ((j + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL));
             if (!ok) break;
             tc_fence_after();
-            issue_st(tmem_base + TM_X, sK, sQ1);        // in order behind dV/dK, which read X
+            issue_st(tmem_base + TM_X, sK, sQ1);
             tc_commit(&bars[BB_S_FULL]);
-            BWD_TS(1, 4);
+            BWD_TS(1, 2);
+          }
+          ok = mbar_wait(&bars[BB_PDS_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL));
+          if (!ok) break;
+          tc_fence_after();
+          BWD_TS(1, 3);
+          issue_dq();                                   // Y: every warp took dP^T out before publishing dS^T
+          tc_commit(&bars[BB_DQ_FULL]);
+          issue_dk(sQ, j == 0);
+          tc_commit(&bars[BB_Q_EMPTY + s]);
+          tc_commit(&bars[BB_DS_FREE]);
+          BWD_TS(1, 4);
+          if (j + 1 < ntot) {
             ok = mbar_wait(&bars[BB_DQ_FREE], j & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE));
             if (!ok) break;
             tc_fence_after();
@@ -461,7 +530,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 17) tmem_dealloc(tmem_base, 512);
+  if (warp == BWD_WARP_MMA) tmem_dealloc(tmem_base, 512);
 }
 
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,

@@ -26,8 +26,8 @@ def main(argv):
     do = torch.randn(B, Hq, sq, 128, device=dev).bfloat16()
     scale = 1.0 / math.sqrt(128.0)
     dq = torch.zeros(B, Hq, sq, 128, device=dev)
-    dk = torch.empty(B, Hkv, skv, 128, device=dev)
-    dv = torch.empty_like(dk)
+    dk = torch.empty(B, Hkv, skv, 128, device=dev, dtype=torch.bfloat16)   # written in the input dtype,
+    dv = torch.empty_like(dk)                                               # as the step loop does
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     for _ in range(iters):
         ev[0].record()
@@ -35,7 +35,7 @@ def main(argv):
         ev[1].record()
         delta = ops.bwd_prep(o, do)
         dq.zero_()
-        ops.bwd_block(q, do, lse, delta, k, v, scale, dq, dk, dv, False)
+        ops.bwd_block(q, do, lse, delta, k, v, scale, dq, dk, dv, "final")
         ev[2].record()
         torch.cuda.synchronize()
     f = 4.0 * B * Hq * 128 * sq * skv

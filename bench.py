@@ -154,11 +154,6 @@ def run_reference(args, cfg):
     print(json.dumps(line), flush=True)
 
 
-def launches_per_step_bwd(world):
-    """Backward-block launches per step: one (all query blocks per pass)."""
-    return 1
-
-
 def workload_name(cid, cfg):
     B, Hq, Hkv, D, Sq, Skv, dt = cfg
     return f"config{cid}: xattn fwd+bwd B={B} Hq={Hq} Hkv={Hkv} D={D} Sq={Sq} Skv={Skv} {dt}, Q and K/V sharded by sequence"
@@ -269,9 +264,11 @@ def main():
     peak = pk["bf16_sustained"]
     roofline = {"bound": "tensor", "kernel": "bwd_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "peak_source": f"{pk['source']} (sustained cuBLAS bf16)",
-                # DRAM bytes per launch: ncu dram__bytes_read+write of one launch at Skv=32768 (324.5 MB, see
-                # profiles/bwd_kernel_sq2048_skv32768.md), K/V-proportional part scaled to this shard
-                "traffic": (268.4e6 * (Skv / world) / 32768 + 56e6) * launches_per_step_bwd(world),
+                # DRAM bytes per launch, from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of one
+                # launch at Sq=2048, Skv=32768: 324.5 MB, of which 268.4 MB is K,V in and dK,dV out (scales with
+                # this rank's key rows) and 56 MB is Q, dO and dQ (all query blocks pass through every rank)
+                "traffic": 268.4e6 * (Skv / world) / 32768 + 56e6 * (Sq / 2048),
+                "traffic_source": "ncu capture at Skv=32768 scaled by key rows",
                 "bwd_kernel_ms_per_step": bwd_ms_step, "fwd_kernel_ms_per_step": fwd_ms_step,
                 "fwd_achieved": (f_fwd / world) / (fwd_ms_step * 1e-3) / 1e12,
                 "launches_per_step": {"fwd": len(prof["fwd"]) // args.steps, "bwd": len(prof["bwd"]) // args.steps}}

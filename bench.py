@@ -280,7 +280,7 @@ def main():
         ho, hdq = torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory()
         hdk, hdv = torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()
 
-        streamer = lvx.HostStreamedAttention(dev, chunks=4)
+        streamer = lvx.HostStreamedAttention(dev, chunks=8)
 
         def step_e2e():
             streamer.step(hq, hk, hv, hdo, scale, ho, hdq, hdk, hdv)

@@ -72,7 +72,10 @@ __device__ long long g_fwd_ts[3 * 8 * 8];
 
 #define FWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x100 | ((role) << 5) | (bar))
 
-template <bool IS_BF16>
+__device__ __forceinline__ void tmem_ldN(uint32_t a, uint32_t (&r)[32]) { tmem_ld32(a, r); }
+__device__ __forceinline__ void tmem_ldN(uint32_t a, uint32_t (&r)[16]) { tmem_ld16(a, r); }
+
+template <bool IS_BF16, int CW>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -142,69 +145,121 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         tc_fence_after();
         if ((warp & 3) == 0) FWD_TS(wg, 0);
-        uint32_t s[4][32];
-        tmem_ld32(tS + 0, s[0]);
-        tmem_ld32(tS + 32, s[1]);
-        tmem_ld32(tS + 64, s[2]);
-        tmem_ld32(tS + 96, s[3]);
-        tc_wait_ld();
-        if ((warp & 3) == 0) FWD_TS(wg, 1);
-        if (j == n - 1 && last_cols < 128) {
+        // Fast path (every tile but the first and a ragged last one): the exponentials are taken against the
+        // running max as it stands, 32 columns at a time while the next 32 are on their way from TMEM, and P is
+        // held in registers. If no row of the warp turns out to need a higher max (the usual case, since the max
+        // is only raised in steps of 2^8) P is stored and the tile is done; the result is the one the exact path
+        // below would give. Otherwise S is still intact in TMEM and the exact path runs.
+        bool done = false;
+        if (j > 0 && !(j == n - 1 && last_cols < 128)) {
+          uint32_t pk[2][32];
+          uint32_t b0[CW], b1[CW];
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+          float sum0 = 0.f, sum1 = 0.f;
+          const float moff = m;
+          auto chunk = [&](const uint32_t (&b)[CW], uint32_t* out) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
+            for (int i = 0; i < CW / 4; ++i) {
+              const float s0 = __uint_as_float(b[4 * i]), s1 = __uint_as_float(b[4 * i + 1]);
+              const float s2 = __uint_as_float(b[4 * i + 2]), s3 = __uint_as_float(b[4 * i + 3]);
+              mx0 = fmaxf(mx0, s0);
+              mx1 = fmaxf(mx1, s1);
+              mx2 = fmaxf(mx2, s2);
+              mx3 = fmaxf(mx3, s3);
+              const float e0 = ex2f(fmaf(s0, c, -moff)), e1 = ex2f(fmaf(s1, c, -moff));
+              const float e2 = ex2f(fmaf(s2, c, -moff)), e3 = ex2f(fmaf(s3, c, -moff));
+              sum0 += e0 + e1;
+              sum1 += e2 + e3;
+              out[2 * i] = IS_BF16 ? pack_bf16x2(e0, e1) : pack_f16x2(e0, e1);
+              out[2 * i + 1] = IS_BF16 ? pack_bf16x2(e2, e3) : pack_f16x2(e2, e3);
+            }
+          };
+          constexpr int NCH = 128 / CW;
+          tmem_ldN(tS + 0, b0);
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (q * 32 + i >= last_cols) s[q][i] = 0xff800000u;  // -inf
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
-          mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
-          mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
-          mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
-        }
-        const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c);
-        // The running max is only raised when it would grow by more than 2^8; P then stays below 256
-        // and the accumulator rarely needs rescaling. (m, l, O) remain mutually consistent.
-        const bool grow = m_new > m + 8.f;
-        float alpha = 1.f;
-        if (grow) {
-          alpha = ex2f(m - m_new);
-          m = m_new;
-          l *= alpha;
-        }
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t o[32];
-            tmem_ld32(tO + q * 32, o);
+          for (int q = 0; q < NCH; q += 2) {
             tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + q * 32, o);
+            tmem_ldN(tS + (q + 1) * CW, b1);
+            chunk(b0, &pk[0][0] + q * (CW / 2));
+            tc_wait_ld();
+            if (q + 2 < NCH) tmem_ldN(tS + (q + 2) * CW, b0);
+            chunk(b1, &pk[0][0] + (q + 1) * (CW / 2));
+          }
+          const float m_seen = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+          const bool keep = m_seen <= m + 8.f;         // false for a NaN as well
+          if (__all_sync(0xffffffffu, keep)) {
+            if ((warp & 3) == 0) FWD_TS(wg, 2);
+            tmem_st32(tS + 0, pk[0]);
+            tmem_st32(tS + 32, pk[1]);
+            l += sum0 + sum1;
+            done = true;
           }
         }
-        if ((warp & 3) == 0) FWD_TS(wg, 2);
-        const float moff = (m == -INFINITY) ? 0.f : m;
-        float sum0 = 0.f, sum1 = 0.f;
+        if (!done) {
+          uint32_t s[4][32];
+          tmem_ld32(tS + 0, s[0]);
+          tmem_ld32(tS + 32, s[1]);
+          tmem_ld32(tS + 64, s[2]);
+          tmem_ld32(tS + 96, s[3]);
+          tc_wait_ld();
+          if ((warp & 3) == 0) FWD_TS(wg, 1);
+          if (j == n - 1 && last_cols < 128) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t pk[32];
+            for (int q = 0; q < 4; ++q)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float a0 = ex2f(fmaf(__uint_as_float(s[2 * h][2 * i]), c, -moff));
-            const float a1 = ex2f(fmaf(__uint_as_float(s[2 * h][2 * i + 1]), c, -moff));
-            const float b0 = ex2f(fmaf(__uint_as_float(s[2 * h + 1][2 * i]), c, -moff));
-            const float b1 = ex2f(fmaf(__uint_as_float(s[2 * h + 1][2 * i + 1]), c, -moff));
-            sum0 += a0 + a1;
-            sum1 += b0 + b1;
-            pk[i] = IS_BF16 ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
-            pk[16 + i] = IS_BF16 ? pack_bf16x2(b0, b1) : pack_f16x2(b0, b1);
+              for (int i = 0; i < 32; ++i)
+                if (q * 32 + i >= last_cols) s[q][i] = 0xff800000u;  // -inf
           }
-          tmem_st32(tS + h * 32, pk);
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
+            mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
+            mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+          }
+          const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c);
+          // The running max is only raised when it would grow by more than 2^8; P then stays below 256
+          // and the accumulator rarely needs rescaling. (m, l, O) remain mutually consistent.
+          const bool grow = m_new > m + 8.f;
+          float alpha = 1.f;
+          if (grow) {
+            alpha = ex2f(m - m_new);
+            m = m_new;
+            l *= alpha;
+          }
+          if (j > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t o[32];
+              tmem_ld32(tO + q * 32, o);
+              tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st32(tO + q * 32, o);
+            }
+          }
+          if ((warp & 3) == 0) FWD_TS(wg, 2);
+          const float moff = (m == -INFINITY) ? 0.f : m;
+          float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a0 = ex2f(fmaf(__uint_as_float(s[2 * h][2 * i]), c, -moff));
+              const float a1 = ex2f(fmaf(__uint_as_float(s[2 * h][2 * i + 1]), c, -moff));
+              const float b0 = ex2f(fmaf(__uint_as_float(s[2 * h + 1][2 * i]), c, -moff));
+              const float b1 = ex2f(fmaf(__uint_as_float(s[2 * h + 1][2 * i + 1]), c, -moff));
+              sum0 += a0 + a1;
+              sum1 += b0 + b1;
+              pk[i] = IS_BF16 ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
+              pk[16 + i] = IS_BF16 ? pack_bf16x2(b0, b1) : pack_f16x2(b0, b1);
+            }
+            tmem_st32(tS + h * 32, pk);
+          }
+          l += sum0 + sum1;
         }
-        l += sum0 + sum1;
         if ((warp & 3) == 0) FWD_TS(wg, 3);
         tc_wait_st();
         tc_fence_before();
@@ -273,7 +328,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
     } else {
       // =========================== MMA issuer ===========================
-      if (lane == 0) {
+      // The whole warp walks the loop and one elected lane issues: with warp-uniform control flow the
+      // descriptor arithmetic stays on the uniform datapath, and the issuing warp needs few issue slots
+      // per MMA (it shares its scheduler with two softmax warps, and the tensor pipe queues little: every
+      // cycle the issuer is late is a cycle the pipe idles).
+      {
         constexpr uint32_t FMT = IS_BF16 ? UMMA_BF16 : UMMA_F16;
         constexpr uint32_t IDESC_QK = umma_idesc(FMT, UMMA_K_MAJOR, UMMA_K_MAJOR, 128, 128);
         constexpr uint32_t IDESC_PV = umma_idesc(FMT, UMMA_K_MAJOR, UMMA_MN_MAJOR, 128, 128);
@@ -285,62 +344,79 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         auto issue_qk = [&](int i, int stage) {
           const uint32_t a_lo = umma_desc_lo(sQ + i * FWD_TILE_BYTES, 16);
           const uint32_t b_lo = umma_desc_lo(sK + stage * FWD_TILE_BYTES, 16);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t off = ((kk >> 2) * FWD_HALF_BYTES + (kk & 3) * 32) >> 4;
-            umma_ss_f16(tmem_base + i * 128, umma_desc_join(a_lo + off, HI), umma_desc_join(b_lo + off, HI), IDESC_QK,
-                        kk > 0);
+            for (int kk = 0; kk < 8; ++kk) {
+              const uint32_t off = ((kk >> 2) * FWD_HALF_BYTES + (kk & 3) * 32) >> 4;
+              umma_ss_f16(tmem_base + i * 128, umma_desc_join(a_lo + off, HI), umma_desc_join(b_lo + off, HI),
+                          IDESC_QK, kk > 0);
+            }
           }
+          __syncwarp();
         };
         auto issue_pv = [&](int i, int stage, bool first) {
           const uint32_t b_lo = umma_desc_lo(sV + stage * FWD_TILE_BYTES, FWD_HALF_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_ts_f16(tmem_base + 256 + i * 128, tmem_base + i * 128 + kk * 8,
-                        umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_PV, (!first) || kk > 0);
+            for (int kk = 0; kk < 8; ++kk)
+              umma_ts_f16(tmem_base + 256 + i * 128, tmem_base + i * 128 + kk * 8,
+                          umma_desc_join(b_lo + ((kk * 2048) >> 4), HI), IDESC_PV, (!first) || kk > 0);
+          }
+          __syncwarp();
+        };
+        auto commit = [&](uint64_t* bar) {
+          if (elect_one()) tc_commit(bar);
+          __syncwarp();
         };
 
         bool ok = mbar_wait(&bars[FB_Q_FULL], 0, abort_flag, p.status, FWD_CODE(3, FB_Q_FULL));
         ok = ok && mbar_wait(&bars[FB_K_FULL + 0], 0, abort_flag, p.status, FWD_CODE(3, FB_K_FULL));
+        ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           tc_fence_after();
           issue_qk(0, 0);
-          tc_commit(&bars[FB_S_FULL + 0]);
+          commit(&bars[FB_S_FULL + 0]);
           issue_qk(1, 0);
-          tc_commit(&bars[FB_S_FULL + 1]);
-          tc_commit(&bars[FB_K_EMPTY + 0]);
+          commit(&bars[FB_S_FULL + 1]);
+          commit(&bars[FB_K_EMPTY + 0]);
         }
         for (int j = 0; ok && j < n; ++j) {
           const int s = j % FWD_NS;
           const uint32_t ph = (j / FWD_NS) & 1;
           const int s1 = (j + 1) % FWD_NS;
           const uint32_t ph1 = ((j + 1) / FWD_NS) & 1;
-          for (int i = 0; i < 2 && ok; ++i) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            if (!ok) break;
             FWD_TS(2, i * 4 + 0);
             ok = mbar_wait(&bars[FB_P_FULL + i], j & 1, abort_flag, p.status, FWD_CODE(3, FB_P_FULL));
             FWD_TS(2, i * 4 + 1);
             if (ok && i == 0) ok = mbar_wait(&bars[FB_V_FULL + s], ph, abort_flag, p.status, FWD_CODE(3, FB_V_FULL));
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
             issue_pv(i, s, j == 0);
             FWD_TS(2, i * 4 + 2);
-            if (i == 1) tc_commit(&bars[FB_V_EMPTY + s]);
+            if (i == 1) commit(&bars[FB_V_EMPTY + s]);
             if (j + 1 < n) {
-              if (i == 0) ok = mbar_wait(&bars[FB_K_FULL + s1], ph1, abort_flag, p.status, FWD_CODE(3, FB_K_FULL));
+              if (i == 0) {
+                ok = mbar_wait(&bars[FB_K_FULL + s1], ph1, abort_flag, p.status, FWD_CODE(3, FB_K_FULL));
+                ok = __all_sync(0xffffffffu, ok);
+              }
               if (!ok) break;
               tc_fence_after();
               issue_qk(i, s1);
               FWD_TS(2, i * 4 + 3);
-              tc_commit(&bars[FB_S_FULL + i]);
-              if (i == 1) tc_commit(&bars[FB_K_EMPTY + s1]);
+              commit(&bars[FB_S_FULL + i]);
+              if (i == 1) commit(&bars[FB_K_EMPTY + s1]);
             } else {
-              tc_commit(&bars[FB_O_DONE + i]);
+              commit(&bars[FB_O_DONE + i]);
             }
           }
         }
         if (!ok) {
           // wind down: let every MMA already issued finish before TMEM is released
-          tc_commit(&bars[FB_DRAIN]);
+          commit(&bars[FB_DRAIN]);
           long long t0 = clock64();
           while (!mbar_try_wait(&bars[FB_DRAIN], 0) && clock64() - t0 < LVX_SPIN_LIMIT_CYCLES) {}
         }
@@ -447,16 +523,14 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   p.debug = getenv("LVX_FWD_DEBUG") ? 1 : 0;
 
   dim3 grid(pl.m_blocks, qb * s.B * s.Hkv, pl.nsplit);
-  cudaError_t e;
-  if (s.dtype == LVX_BF16) {
-    e = cudaFuncSetAttribute(fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fwd)");
-    fwd_kernel<true><<<grid, FWD_THREADS, FWD_SMEM, st>>>(tmQ, tmK, tmV, p);
-  } else {
-    e = cudaFuncSetAttribute(fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fwd)");
-    fwd_kernel<false><<<grid, FWD_THREADS, FWD_SMEM, st>>>(tmQ, tmK, tmV, p);
-  }
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kern) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+    if (e == cudaSuccess) kern<<<grid, FWD_THREADS, FWD_SMEM, st>>>(tmQ, tmK, tmV, p);
+  };
+  if (s.dtype == LVX_BF16) go(fwd_kernel<true, 32>);
+  else go(fwd_kernel<false, 32>);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fwd)");
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_kernel launch");
   if (p.debug) {

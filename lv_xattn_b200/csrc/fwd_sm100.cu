@@ -75,7 +75,7 @@ __device__ long long g_fwd_ts[3 * 8 * 8];
 __device__ __forceinline__ void tmem_ldN(uint32_t a, uint32_t (&r)[32]) { tmem_ld32(a, r); }
 __device__ __forceinline__ void tmem_ldN(uint32_t a, uint32_t (&r)[16]) { tmem_ld16(a, r); }
 
-template <bool IS_BF16, int CW>
+template <bool IS_BF16, int CW, int POLY>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -154,22 +154,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (j > 0 && !(j == n - 1 && last_cols < 128)) {
           uint32_t pk[2][32];
           uint32_t b0[CW], b1[CW];
-          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-          float sum0 = 0.f, sum1 = 0.f;
-          const float moff = m;
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+          uint64_t sum_a = f32x2(0.f, 0.f), sum_b = f32x2(0.f, 0.f);
+          const uint64_t c2 = f32x2(c, c), nm2 = f32x2(-m, -m);
           auto chunk = [&](const uint32_t (&b)[CW], uint32_t* out) {
 #pragma unroll
             for (int i = 0; i < CW / 4; ++i) {
               const float s0 = __uint_as_float(b[4 * i]), s1 = __uint_as_float(b[4 * i + 1]);
               const float s2 = __uint_as_float(b[4 * i + 2]), s3 = __uint_as_float(b[4 * i + 3]);
-              mx0 = fmaxf(mx0, s0);
-              mx1 = fmaxf(mx1, s1);
-              mx2 = fmaxf(mx2, s2);
-              mx3 = fmaxf(mx3, s3);
-              const float e0 = ex2f(fmaf(s0, c, -moff)), e1 = ex2f(fmaf(s1, c, -moff));
-              const float e2 = ex2f(fmaf(s2, c, -moff)), e3 = ex2f(fmaf(s3, c, -moff));
-              sum0 += e0 + e1;
-              sum1 += e2 + e3;
+              mx0 = max3f(mx0, s0, s1);
+              mx1 = max3f(mx1, s2, s3);
+              float x0, x1, e2, e3;
+              f32x2_get(fma2(f32x2(s0, s1), c2, nm2), x0, x1);
+              const uint64_t xb = fma2(f32x2(s2, s3), c2, nm2);
+              const float e0 = ex2f(x0), e1 = ex2f(x1);
+              if (POLY == 2 || (POLY == 1 && (i & 1) == 0)) {
+                ex2_poly2(xb, e2, e3);
+              } else {
+                float x2, x3;
+                f32x2_get(xb, x2, x3);
+                e2 = ex2f(x2);
+                e3 = ex2f(x3);
+              }
+              sum_a = add2(sum_a, f32x2(e0, e1));
+              sum_b = add2(sum_b, f32x2(e2, e3));
               out[2 * i] = IS_BF16 ? pack_bf16x2(e0, e1) : pack_f16x2(e0, e1);
               out[2 * i + 1] = IS_BF16 ? pack_bf16x2(e2, e3) : pack_f16x2(e2, e3);
             }
@@ -185,13 +193,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (q + 2 < NCH) tmem_ldN(tS + (q + 2) * CW, b0);
             chunk(b1, &pk[0][0] + (q + 1) * (CW / 2));
           }
-          const float m_seen = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * c;
+          const float m_seen = fmaxf(mx0, mx1) * c;
           const bool keep = m_seen <= m + 8.f;         // false for a NaN as well
           if (__all_sync(0xffffffffu, keep)) {
             if ((warp & 3) == 0) FWD_TS(wg, 2);
             tmem_st32(tS + 0, pk[0]);
             tmem_st32(tS + 32, pk[1]);
-            l += sum0 + sum1;
+            float t0, t1, t2, t3;
+            f32x2_get(sum_a, t0, t1);
+            f32x2_get(sum_b, t2, t3);
+            l += (t0 + t1) + (t2 + t3);
             done = true;
           }
         }
@@ -528,8 +539,15 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
     if (e == cudaSuccess) kern<<<grid, FWD_THREADS, FWD_SMEM, st>>>(tmQ, tmK, tmV, p);
   };
-  if (s.dtype == LVX_BF16) go(fwd_kernel<true, 32>);
-  else go(fwd_kernel<false, 32>);
+  const char* pe = getenv("LVX_FWD_POLY");
+  const int poly = pe ? atoi(pe) : 0;
+  if (s.dtype == LVX_BF16) {
+    if (poly == 2) go(fwd_kernel<true, 32, 2>);
+    else if (poly == 1) go(fwd_kernel<true, 32, 1>);
+    else go(fwd_kernel<true, 32, 0>);
+  } else {
+    go(fwd_kernel<false, 32, 0>);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fwd)");
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_kernel launch");

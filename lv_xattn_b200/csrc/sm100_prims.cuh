@@ -310,36 +310,6 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
-  uint64_t d;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
-  return d;
-}
-// 2^x for two values on the FMA pipe instead of the special-function unit (16 results per clock per SM, the
-// bottleneck of the softmax): round x to the nearest integer j with the 1.5*2^23 trick, a cubic for 2^(x-j) on
-// [-0.5, 0.5] (relative error 7.5e-5, far below the rounding of the 16-bit P it feeds), then j is added into
-// the exponent field. x must be below 2^22 in magnitude; results below 2^-125 are clamped there.
-__device__ __forceinline__ void ex2_poly2(uint64_t x, float& e0, float& e1) {
-  float x0, x1;
-  f32x2_get(x, x0, x1);
-  const uint64_t xc = f32x2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-  const uint64_t magic = f32x2(12582912.f, 12582912.f);
-  const uint64_t xr = add2(xc, magic);
-  const uint64_t f = sub2(xc, sub2(xr, magic));
-  uint64_t p = fma2(f, f32x2(0.0551716648f, 0.0551716648f), f32x2(0.2426111251f, 0.2426111251f));
-  p = fma2(p, f, f32x2(0.6932609677f, 0.6932609677f));
-  p = fma2(p, f, f32x2(0.9999280572f, 0.9999280572f));
-  float p0, p1, r0, r1;
-  f32x2_get(p, p0, p1);
-  f32x2_get(xr, r0, r1);
-  e0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(r0) << 23));
-  e1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(r1) << 23));
-}
-__device__ __forceinline__ float max3f(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -149,6 +149,43 @@ int lvx_fwd_block_static(const lvx_shape* s, const void* q, const void* k, const
                          const int32_t* kv_valid_len, float sm_scale, void* o_out, float* lse_out,
                          void* stream);
 
+/* ---- Exchange over peer-mapped memory (NVLink / NVSwitch) ------------------------------------------------
+ * The reference moves blocks between ranks with torch.distributed batch_isend_irecv
+ * (lv_xattn/async_communication.py:138-233) and reduces after each hop. These entry points do the same
+ * exchanges with the library's own kernels reading the peers' memory directly; they need one buffer per
+ * rank that every rank of the group has mapped (CUDA IPC / VMM; the Python host side uses torch's symmetric
+ * memory). `lvx_peers.ptr[s]` is the address, in THIS process, of rank s's copy of that buffer; all copies
+ * have the same layout. Ordering uses a flag array of LVX_P2P_SLOTS x LVX_MAX_PEERS uint32 words per rank in
+ * such a buffer, zero at start: the producer calls lvx_p2p_signal(flags, slot, epoch) after the kernels that
+ * fill its buffer (same stream), which stores `epoch` into word [slot][rank] of every peer's array; a pulling
+ * call names its own array (`my_flags`, a device pointer), the slot and the epoch it needs and waits inside
+ * the kernel, at most a few seconds, for all `world` words -- on time-out it reads nothing, and
+ * lvx_device_status() returns 0x1300 | peer. Epochs of a slot must increase by one per use (compared
+ * modulo 2^32); a buffer may be rewritten two epochs after it was signalled, so callers alternate two. */
+#define LVX_MAX_PEERS 16
+#define LVX_P2P_SLOTS 8
+typedef struct lvx_peers {
+  int32_t world;                      /* ranks in the group (<= LVX_MAX_PEERS) */
+  int32_t rank;                       /* this rank */
+  const void* ptr[LVX_MAX_PEERS];     /* ptr[s]: rank s's buffer as mapped in this process (16-byte aligned) */
+} lvx_peers;
+
+/* Publishes `epoch` for `slot` to every rank (stream-ordered after the producer kernels). */
+int lvx_p2p_signal(const lvx_peers* flags, int slot, uint32_t epoch, void* stream);
+/* All-gather by pulling: dst + s*dst_stride <- rank s's bytes [src_offset, src_offset+bytes) for every s
+ * (this rank included). Replaces send_recv_fwd_q / the backward slab exchange of the reference
+ * (lv_xattn/async_communication.py:138-169) when every rank needs every block. */
+int lvx_p2p_gather(const lvx_peers* src, size_t src_offset, size_t bytes, void* dst, size_t dst_stride,
+                   const uint32_t* my_flags, int slot, uint32_t epoch, void* stream);
+/* lvx_fwd_merge_parts with partial c read from rank c's buffer: O fp32 [B*Hq*Sq*D] at byte o_offset, lse
+ * fp32 [B*Hq*Sq] at byte lse_offset (the offsets select this rank's block inside the peers' buffers).
+ * shape describes ONE block (q_blocks ignored). */
+int lvx_p2p_fwd_merge(const lvx_shape* s, const lvx_peers* parts, size_t o_offset, size_t lse_offset, void* o_out,
+                      float* lse_out, const uint32_t* my_flags, int slot, uint32_t epoch, void* stream);
+/* lvx_sum_cast with partial c read from rank c's buffer at byte `offset` (n fp32 elements each). */
+int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_dtype, size_t n,
+                     const uint32_t* my_flags, int slot, uint32_t epoch, void* stream);
+
 /* Self-test of the tensor-core building blocks (TMA tile load, shared-memory and TMEM operand
  * descriptors, TMEM load/store): runs one 128 x N x K product in the operand arrangement `mode`
  * and writes D (fp32 [128,N]) to `d_out`. a/b are device buffers in the arrangement the mode

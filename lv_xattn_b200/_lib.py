@@ -21,11 +21,18 @@ SYMBOLS = [
     "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_query_workspace", "lvx_fwd_block",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
     "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
+    "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast",
 ]
+MAX_PEERS = 16      # LVX_MAX_PEERS
+P2P_SLOTS = 8       # LVX_P2P_SLOTS
 
 
 class LvxShape(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("B", "Hq", "Hkv", "Sq", "Skv", "D", "dtype", "q_blocks")]
+
+
+class LvxPeers(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("ptr", ctypes.c_void_p * 16)]
 
 
 class LvxError(RuntimeError):

@@ -48,9 +48,11 @@ def _schedule(schedule):
     """"gather" (default): every rank fetches all W query blocks, makes ONE pass over its K/V shard and the
     partial results are exchanged and reduced at home -- one kernel launch per pass, dK/dV written once.
     "ring": the reference's step loop, one query block per step with travelling accumulators
-    (lv_xattn/attn.py:364-429). Both move the same bytes per GPU; LVX_SCHEDULE overrides the default."""
+    (lv_xattn/attn.py:364-429). "p2p": the "gather" schedule with every exchange done by the library's own
+    kernels over peer-mapped memory instead of NCCL calls (peer_memory.py; CUDA devices of one NVLink domain
+    only). All move the same bytes per GPU; LVX_SCHEDULE overrides the default."""
     s = schedule or os.environ.get("LVX_SCHEDULE", "gather")
-    if s not in ("gather", "ring"):
+    if s not in ("gather", "ring", "p2p"):
         raise ValueError(f"unknown schedule {s!r}")
     return s
 
@@ -122,6 +124,31 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         return q, k, v, o, L
 
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
+    if _schedule(schedule) == "p2p":
+        from . import peer_memory as pm
+        rank = pm.get_sequence_parallel_rank()
+        flag_peers, my_flags = pm.get_flags(dev)
+        # the Q block is published in a peer-mapped buffer and every rank pulls all W of them
+        e = pm.next_epoch(pm.SLOT_FWD_Q)
+        qbuf = pm.get_peer_buffer("p2p_q", 2 * n_o * es, dev)
+        q_off = (e & 1) * n_o * es
+        _carve(qbuf.local, q_off, (B, Hq, Sq, D), dt).copy_(qc)
+        ops.p2p_signal(flag_peers, pm.SLOT_FWD_Q, e)
+        q_all = _carve(get_slabs("g_q", W * n_o * es, dev, 1)[0], 0, (W, B, Hq, Sq, D), dt)
+        ops.p2p_gather(qbuf.peers, q_off, n_o * es, q_all, my_flags, pm.SLOT_FWD_Q, e)
+        part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl)
+        # the W partial (O, lse) blocks stay here; each owner merges its block straight out of the peers' memory
+        e = pm.next_epoch(pm.SLOT_FWD_PARTS)
+        blk = W * (n_o + n_l) * 4
+        pbuf = pm.get_peer_buffer("p2p_parts", 2 * blk, dev)
+        p_off = (e & 1) * blk
+        o_parts = _carve(pbuf.local, p_off, (W, B, Hq, Sq, D), torch.float32)
+        l_parts = _carve(pbuf.local, p_off + W * n_o * 4, (W * B * Hq, Sq), torch.float32)
+        ops.fwd_combine(part, None, None, o_parts, l_parts, False)
+        ops.p2p_signal(flag_peers, pm.SLOT_FWD_PARTS, e)
+        ops.p2p_fwd_merge(pbuf.peers, p_off + rank * n_o * 4, p_off + W * n_o * 4 + rank * n_l * 4, o, L, my_flags,
+                          pm.SLOT_FWD_PARTS, e)
+        return q, k, v, o, L
     if _schedule(schedule) == "gather":
         q_all = _carve(get_slabs("g_q", W * n_o * es, dev, 1)[0], 0, (W, B, Hq, Sq, D), dt)
         wait_async_handles(all_gather_blocks([qc], [q_all], comm_mode))
@@ -216,6 +243,41 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             dq_acc.zero_()
             ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl)
         ops.add_cast(dq_acc, None, dt, out=dq)
+        return dq, dk, dv
+    elif _schedule(schedule) == "p2p":
+        from . import peer_memory as pm
+        if (n_r * 4) % 16:
+            raise ValueError("the p2p schedule needs B*Hq*Sq to be a multiple of 4")
+        rank = pm.get_sequence_parallel_rank()
+        flag_peers, my_flags = pm.get_flags(dev)
+        e = pm.next_epoch(pm.SLOT_BWD_IN)
+        blk = 2 * n_q * es + 2 * n_r * 4
+        ibuf = pm.get_peer_buffer("p2p_bwd_in", 2 * blk, dev)
+        base = (e & 1) * blk
+        offs = (base, base + n_q * es, base + 2 * n_q * es, base + 2 * n_q * es + n_r * 4)
+        _carve(ibuf.local, offs[0], (B, Hq, Sq, D), dt).copy_(qc)
+        _carve(ibuf.local, offs[1], (B, Hq, Sq, D), dt).copy_(doc)
+        _carve(ibuf.local, offs[2], (B * Hq, Sq), torch.float32).copy_(Lc)
+        _carve(ibuf.local, offs[3], (B * Hq, Sq), torch.float32).copy_(delta)
+        ops.p2p_signal(flag_peers, pm.SLOT_BWD_IN, e)
+        gbuf = get_slabs("g_bwd_in", W * blk, dev, 1)[0]
+        q_all = _carve(gbuf, 0, (W, B, Hq, Sq, D), dt)
+        do_all = _carve(gbuf, W * n_q * es, (W, B, Hq, Sq, D), dt)
+        l_all = _carve(gbuf, 2 * W * n_q * es, (W * B * Hq, Sq), torch.float32)
+        d_all = _carve(gbuf, 2 * W * n_q * es + W * n_r * 4, (W * B * Hq, Sq), torch.float32)
+        for dst, off, nb in ((q_all, offs[0], n_q * es), (do_all, offs[1], n_q * es), (l_all, offs[2], n_r * 4),
+                             (d_all, offs[3], n_r * 4)):
+            ops.p2p_gather(ibuf.peers, off, nb, dst, my_flags, pm.SLOT_BWD_IN, e)
+        e = pm.next_epoch(pm.SLOT_BWD_DQ)
+        dbuf = pm.get_peer_buffer("p2p_dq", 2 * W * n_q * 4, dev)
+        d_off = (e & 1) * W * n_q * 4
+        dq_parts = _carve(dbuf.local, d_off, (W, B, Hq, Sq, D), torch.float32)
+        dq_parts.zero_()
+        dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        ops.bwd_block(q_all, do_all, l_all, d_all, kc, vc, sm_scale, dq_parts, dk, dv, "final", kvl)
+        ops.p2p_signal(flag_peers, pm.SLOT_BWD_DQ, e)
+        ops.p2p_sum_cast(dbuf.peers, d_off + rank * n_q * 4, dq, my_flags, pm.SLOT_BWD_DQ, e)   # each owner sums its block
         return dq, dk, dv
     elif _schedule(schedule) == "gather":
         gbuf = get_slabs("g_bwd_in", W * (2 * n_q * es + 2 * n_r * 4), dev, 1)[0]

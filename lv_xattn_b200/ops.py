@@ -237,6 +237,51 @@ def sum_cast(parts, out_dtype, out=None):
     return out
 
 
+# ---- exchange over peer-mapped memory (see peer_memory.py for the buffers) ---------------------------------
+def p2p_signal(flags_peers, slot: int, epoch: int):
+    """Publishes `epoch` for `slot` to every rank, ordered after the kernels already on the current stream."""
+    lib = _lib.load()
+    _lib.check(lib.lvx_p2p_signal(ctypes.byref(flags_peers), slot, ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()),
+               "lvx_p2p_signal")
+    _count()
+
+
+def p2p_gather(src_peers, src_offset: int, nbytes: int, dst, my_flags, slot: int, epoch: int):
+    """dst[s] <- rank s's bytes [src_offset, src_offset + nbytes) for every rank s; dst is a contiguous
+    [W, ...] tensor whose blocks are nbytes long."""
+    _require_cuda(dst, my_flags)
+    lib = _lib.load()
+    W = src_peers.world
+    if dst.numel() * dst.element_size() != W * nbytes or not dst.is_contiguous():
+        raise ValueError("p2p_gather: dst must be a contiguous [W, ...] tensor of W blocks of nbytes")
+    _lib.check(lib.lvx_p2p_gather(ctypes.byref(src_peers), ctypes.c_size_t(src_offset), ctypes.c_size_t(nbytes),
+                                  _lib.ptr(dst), ctypes.c_size_t(nbytes), _lib.ptr(my_flags), slot,
+                                  ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()), "lvx_p2p_gather")
+    _count()
+
+
+def p2p_fwd_merge(parts_peers, o_offset: int, lse_offset: int, o_out, lse_out, my_flags, slot: int, epoch: int):
+    """fwd_merge_parts with partial c read from rank c's buffer (O fp32 at byte o_offset, lse at lse_offset)."""
+    _require_cuda(o_out, lse_out, my_flags)
+    lib = _lib.load()
+    B, Hq, Sq, D = o_out.shape
+    shp = _lib.make_shape(B, Hq, Hq, Sq, 0, D, o_out.dtype)
+    _lib.check(lib.lvx_p2p_fwd_merge(ctypes.byref(shp), ctypes.byref(parts_peers), ctypes.c_size_t(o_offset),
+                                     ctypes.c_size_t(lse_offset), _lib.ptr(o_out), _lib.ptr(lse_out), _lib.ptr(my_flags),
+                                     slot, ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()), "lvx_p2p_fwd_merge")
+    _count()
+
+
+def p2p_sum_cast(parts_peers, offset: int, out, my_flags, slot: int, epoch: int):
+    """out <- cast(sum over ranks c of the fp32 block at byte `offset` of rank c's buffer)."""
+    _require_cuda(out, my_flags)
+    lib = _lib.load()
+    _lib.check(lib.lvx_p2p_sum_cast(ctypes.byref(parts_peers), ctypes.c_size_t(offset), _lib.ptr(out),
+                                    _lib.dtype_code(out.dtype), ctypes.c_size_t(out.numel()), _lib.ptr(my_flags), slot,
+                                    ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()), "lvx_p2p_sum_cast")
+    _count()
+
+
 def add_cast(a, b, out_dtype, out=None):
     """cast(a + b) for fp32 a (and optional fp32 b of the same shape); written into `out` when given."""
     _require_cuda(a, b)

@@ -1,0 +1,92 @@
+"""Peer-mapped buffers of the sequence-parallel group, for the exchange steps that the library's own kernels do
+over NVLink (`schedule="p2p"`): one buffer per role on every rank, mapped into every other rank's address space
+through torch's symmetric memory (CUDA VMM handles exchanged over the group's store), plus the flag array of the
+signal/wait protocol (csrc/p2p.cu).
+
+Nothing here has a counterpart in the reference, which sends every block through NCCL point-to-point calls
+(lv_xattn/async_communication.py:138-233).
+
+Every rank must create the same buffers in the same order (creation is a collective). Multicast (NVLS) binding of
+the buffers is switched off: only plain peer loads and stores are used.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .async_communication import get_sequence_parallel_group, get_sequence_parallel_rank, get_sequence_parallel_size
+
+SLOT_FWD_Q, SLOT_FWD_PARTS, SLOT_BWD_IN, SLOT_BWD_DQ = 0, 1, 2, 3
+
+_BUFFERS = {}
+_FLAGS = None
+_EPOCHS = [0] * _lib.P2P_SLOTS
+
+
+class PeerBuffer:
+    """`local`: this rank's buffer (uint8 tensor); `peers`: the LvxPeers table of every rank's copy."""
+
+    def __init__(self, nbytes: int, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = get_sequence_parallel_group()
+        W = get_sequence_parallel_size()
+        if W > _lib.MAX_PEERS:
+            raise ValueError(f"at most {_lib.MAX_PEERS} ranks can share peer buffers")
+        self.nbytes = nbytes
+        self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        handle = symm_mem.rendezvous(self.local, group)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+        if len(ptrs) != W or ptrs[get_sequence_parallel_rank()] != self.local.data_ptr():
+            raise RuntimeError("symmetric-memory rendezvous returned an unexpected peer table")
+        self._handle = handle          # keeps the mappings alive
+        self.peers = _lib.LvxPeers()
+        self.peers.world, self.peers.rank = W, get_sequence_parallel_rank()
+        for i, a in enumerate(ptrs):
+            self.peers.ptr[i] = a
+
+
+def _ensure_env():
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+
+def get_peer_buffer(name: str, nbytes: int, device) -> PeerBuffer:
+    """Buffer for role `name`, at least nbytes long; re-created (collectively) when it has to grow."""
+    _ensure_env()
+    key = (name, str(device))
+    buf = _BUFFERS.get(key)
+    if buf is None or buf.nbytes < nbytes:
+        n = (max(nbytes, 4096) + 4095) // 4096 * 4096
+        buf = PeerBuffer(n, device)
+        _BUFFERS[key] = buf
+    return buf
+
+
+def get_flags(device):
+    """(peer table of the flag arrays, this rank's flag array as an int32 tensor)."""
+    global _FLAGS
+    _ensure_env()
+    if _FLAGS is None:
+        buf = PeerBuffer(4096, device)
+        buf.local.zero_()
+        torch.cuda.current_stream(device).synchronize()
+        dist.barrier(group=get_sequence_parallel_group())     # nobody signals before every array is zero
+        _FLAGS = (buf, buf.local.view(torch.int32))
+    return _FLAGS[0].peers, _FLAGS[1]
+
+
+def next_epoch(slot: int) -> int:
+    _EPOCHS[slot] += 1
+    return _EPOCHS[slot]
+
+
+def reset_peer_memory():
+    """Forgets every buffer (collective: all ranks must call it together, with no exchange in flight)."""
+    global _FLAGS
+    _BUFFERS.clear()
+    _FLAGS = None
+    for i in range(len(_EPOCHS)):
+        _EPOCHS[i] = 0

@@ -1,4 +1,5 @@
-"""One NCCL rank of tests/test_gpu_multi.py (launched by torch.distributed.run)."""
+"""One NCCL rank of tests/test_gpu_multi.py (launched by torch.distributed.run).
+argv[1]: comma-separated schedules to run and compare (default "gather,ring")."""
 import math
 import os
 import sys
@@ -16,6 +17,7 @@ torch.cuda.set_device(local)
 dev = torch.device("cuda", local)
 lvx.initialize_distributed("nccl")
 scale = 1.0 / math.sqrt(128.0)
+schedules = (sys.argv[1] if len(sys.argv) > 1 else "gather,ring").split(",")
 cases = [
     (1, 8, 2, 128 * world, 1024 * world, torch.bfloat16, None),
     (2, 4, 2, 64 * world, 512 * world, torch.bfloat16, [512 * world, 512 * world * 3 // 4]),
@@ -25,15 +27,15 @@ for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
     q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 31, dtype)
     o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, scale, valid)
     ql, dol, kl, vl = (orc.shard(t, rank, world).to(dev) for t in (q, do, k, v))
-    for rep in range(2):
-        sched = ("gather", "ring")[rep]
+    torch.distributed.barrier()          # the oracle above takes a different time on every rank
+    for rep, sched in enumerate(schedules):
         _, _, _, o, L = lvx._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid, schedule=sched)
         dq, dk, dv = lvx._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid,
                                         schedule=sched)
         if rep == 0:
             first = [t.clone() for t in (o, L, dq, dk, dv)]
-    for a, b in zip(first, (o, L, dq, dk, dv)):      # both schedules compute the same thing
-        assert (a.float() - b.float()).abs().max().item() <= (1e-4 if dtype == torch.float32 else 2e-2)
+        for a, b in zip(first, (o, L, dq, dk, dv)):      # every schedule computes the same thing
+            assert (a.float() - b.float()).abs().max().item() <= (1e-4 if dtype == torch.float32 else 2e-2), sched
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     Sl = Sq // world

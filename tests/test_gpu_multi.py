@@ -11,13 +11,25 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_ring_nccl(world):
+def _run(world, schedules, port):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), os.path.join(ROOT, "tests", "_multi_gpu_worker.py")]
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "_multi_gpu_worker.py"),
+           schedules]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert r.stdout.count("RANK_OK") == world, r.stdout[-3000:]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ring_nccl(world):
+    _run(world, "gather,ring", 29600 + world)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_memory_schedule(world):
+    """The exchanges done by the library's own kernels over peer-mapped memory, twice in a row (both buffers of
+    every slot), against the NCCL schedule and the oracle."""
+    _run(world, "gather,p2p,p2p,p2p", 29650 + world)

@@ -78,6 +78,30 @@ def get_flags(device):
     return _FLAGS[0].peers, _FLAGS[1]
 
 
+_AVAILABLE = None
+
+
+def peer_memory_available(device) -> bool:
+    """True when every rank of the group could map the flag arrays (decided once, collectively, so that all
+    ranks pick the same schedule). A failure on any rank -- no peer access, symmetric memory not supported by
+    the driver, more than MAX_PEERS ranks -- makes it False everywhere, with the reason in a warning."""
+    global _AVAILABLE
+    if _AVAILABLE is None:
+        ok = 1
+        try:
+            if dist.get_backend(get_sequence_parallel_group()) != "nccl":
+                raise RuntimeError("the process group is not NCCL")
+            get_flags(device)
+        except Exception as e:  # noqa: BLE001 - any failure means "use the NCCL schedule"
+            import warnings
+            warnings.warn(f"peer-mapped exchange unavailable, using NCCL collectives instead: {e}")
+            ok = 0
+        t = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=get_sequence_parallel_group())
+        _AVAILABLE = bool(t.item())
+    return _AVAILABLE
+
+
 def next_epoch(slot: int) -> int:
     _EPOCHS[slot] += 1
     return _EPOCHS[slot]
@@ -85,8 +109,9 @@ def next_epoch(slot: int) -> int:
 
 def reset_peer_memory():
     """Forgets every buffer (collective: all ranks must call it together, with no exchange in flight)."""
-    global _FLAGS
+    global _FLAGS, _AVAILABLE
     _BUFFERS.clear()
     _FLAGS = None
+    _AVAILABLE = None
     for i in range(len(_EPOCHS)):
         _EPOCHS[i] = 0

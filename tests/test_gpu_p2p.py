@@ -1,0 +1,93 @@
+"""The peer-memory exchange entry points (include/lvx.h, lvx_p2p_*) on ONE GPU: the "ranks" are separate buffers
+of the same device, every signal is launched before the kernel that waits for it (same stream), so no kernel
+ever waits for a later launch. Checks the gather, the partial-(O, lse) merge and the dQ sum against torch."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _peers(tensors, rank):
+    from lv_xattn_b200 import _lib
+    p = _lib.LvxPeers()
+    p.world, p.rank = len(tensors), rank
+    for i, t in enumerate(tensors):
+        p.ptr[i] = t.data_ptr()
+    return p
+
+
+@pytest.fixture()
+def dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("world", [1, 3, 8])
+def test_gather_merge_sum(dev, world):
+    from lv_xattn_b200 import _lib, ops
+    torch.manual_seed(world)
+    B, Hq, Sq, D = 1, 4, 96, 128
+    n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
+    flags = [torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=dev) for _ in range(world)]
+    # ---- gather: rank s owns block s ----
+    nbytes = n_o * 2
+    bufs = [torch.randn(n_o, device=dev).bfloat16() for _ in range(world)]
+    for epoch in (1, 2):
+        for r in range(world):
+            ops.p2p_signal(_peers(flags, r), 0, epoch)
+        for r in range(world):
+            dst = torch.zeros(world, n_o, dtype=torch.bfloat16, device=dev)
+            ops.p2p_gather(_peers(bufs, r), 0, nbytes, dst, flags[r], 0, epoch)
+            assert torch.equal(dst, torch.stack(bufs))
+    # ---- merge: rank c holds partials for every block; block r is merged by rank r ----
+    blk = world * (n_o + n_l) * 4
+    parts = [torch.zeros(blk, dtype=torch.uint8, device=dev) for _ in range(world)]
+    o_p = torch.randn(world, world, n_o, device=dev)                      # [holder c][block r]
+    l_p = torch.randn(world, world, n_l, device=dev) * 3
+    if world > 1:
+        l_p[0, :, :5] = float("-inf")                                     # a holder with nothing valid for some rows
+    for c in range(world):
+        parts[c][: world * n_o * 4].view(torch.float32).view(world, n_o).copy_(o_p[c])
+        parts[c][world * n_o * 4:].view(torch.float32).view(world, n_l).copy_(l_p[c])
+    for r in range(world):
+        ops.p2p_signal(_peers(flags, r), 1, 1)
+    for r in range(world):
+        o = torch.empty(B, Hq, Sq, D, dtype=torch.float32, device=dev)
+        lse = torch.empty(B * Hq, Sq, dtype=torch.float32, device=dev)
+        ops.p2p_fwd_merge(_peers(parts, r), r * n_o * 4, world * n_o * 4 + r * n_l * 4, o, lse, flags[r], 1, 1)
+        lr = l_p[:, r]                                                    # [world, n_l]
+        ref_l = torch.logsumexp(lr, dim=0)
+        w = torch.exp(lr - ref_l).nan_to_num(0.0)
+        ref_o = (o_p[:, r].view(world, n_l, D) * w[:, :, None]).sum(0)
+        assert (lse.view(-1) - ref_l).abs().max().item() < 1e-5
+        assert (o.view(n_l, D) - ref_o).abs().max().item() < 1e-5
+    # ---- sum: dQ partials ----
+    dq_parts = [torch.randn(world, n_o, device=dev) for _ in range(world)]
+    for r in range(world):
+        ops.p2p_signal(_peers(flags, r), 2, 1)
+    for r in range(world):
+        out = torch.empty(B, Hq, Sq, D, dtype=torch.bfloat16, device=dev)
+        ops.p2p_sum_cast(_peers(dq_parts, r), r * n_o * 4, out, flags[r], 2, 1)
+        ref = torch.stack([dq_parts[c][r] for c in range(world)]).sum(0)
+        assert (out.view(-1).float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+def test_argument_checks(dev):
+    from lv_xattn_b200 import _lib, ops
+    flags = torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=dev)
+    buf = torch.zeros(256, dtype=torch.uint8, device=dev)
+    p = _peers([buf], 0)
+    with pytest.raises(_lib.LvxError):
+        ops.p2p_signal(p, _lib.P2P_SLOTS, 1)                 # slot out of range
+    p.world = _lib.MAX_PEERS + 1
+    with pytest.raises(_lib.LvxError):
+        ops.p2p_signal(p, 0, 1)                              # too many peers
+    p = _peers([buf], 0)
+    dst = torch.zeros(1, 24, dtype=torch.uint8, device=dev)
+    with pytest.raises(_lib.LvxError):
+        ops.p2p_gather(p, 0, 24, dst, flags, 0, 1)           # not a multiple of 16 bytes

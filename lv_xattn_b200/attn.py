@@ -44,14 +44,24 @@ from .async_communication import (
 _SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
 
 
-def _schedule(schedule):
+_DEFAULT_SCHEDULE = "gather"
+
+
+def _schedule(schedule, like=None):
     """"gather" (default): every rank fetches all W query blocks, makes ONE pass over its K/V shard and the
     partial results are exchanged and reduced at home -- one kernel launch per pass, dK/dV written once.
     "ring": the reference's step loop, one query block per step with travelling accumulators
     (lv_xattn/attn.py:364-429). "p2p": the "gather" schedule with every exchange done by the library's own
     kernels over peer-mapped memory instead of NCCL calls (peer_memory.py; CUDA devices of one NVLink domain
     only). All move the same bytes per GPU; LVX_SCHEDULE overrides the default."""
-    s = schedule or os.environ.get("LVX_SCHEDULE", "gather")
+    s = schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)
+    if s == "auto":
+        # p2p where every rank can map its peers' memory (decided once, collectively), NCCL collectives otherwise
+        s = "gather"
+        if like is not None and like.is_cuda and get_sequence_parallel_size() > 1:
+            from .peer_memory import peer_memory_available
+            if peer_memory_available(like.device):
+                s = "p2p"
     if s not in ("gather", "ring", "p2p"):
         raise ValueError(f"unknown schedule {s!r}")
     return s
@@ -124,7 +134,8 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         return q, k, v, o, L
 
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
-    if _schedule(schedule) == "p2p":
+    sched = _schedule(schedule, q)
+    if sched == "p2p":
         from . import peer_memory as pm
         rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
@@ -149,7 +160,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         ops.p2p_fwd_merge(pbuf.peers, p_off + rank * n_o * 4, p_off + W * n_o * 4 + rank * n_l * 4, o, L, my_flags,
                           pm.SLOT_FWD_PARTS, e)
         return q, k, v, o, L
-    if _schedule(schedule) == "gather":
+    if sched == "gather":
         q_all = _carve(get_slabs("g_q", W * n_o * es, dev, 1)[0], 0, (W, B, Hq, Sq, D), dt)
         wait_async_handles(all_gather_blocks([qc], [q_all], comm_mode))
         part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl)
@@ -235,6 +246,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
     dv_acc = _carve(acc, n_kv * 4, (B, Hkv, Skv, D), torch.float32)
     dq = torch.empty(B, Hq, Sq, D, dtype=dt, device=dev)
 
+    sched = _schedule(schedule, q) if W > 1 else "gather"
     if W == 1 or comm_mode == "nocomm":
         dq_acc = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
         dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
@@ -244,7 +256,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl)
         ops.add_cast(dq_acc, None, dt, out=dq)
         return dq, dk, dv
-    elif _schedule(schedule) == "p2p":
+    elif sched == "p2p":
         from . import peer_memory as pm
         if (n_r * 4) % 16:
             raise ValueError("the p2p schedule needs B*Hq*Sq to be a multiple of 4")
@@ -279,7 +291,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         ops.p2p_signal(flag_peers, pm.SLOT_BWD_DQ, e)
         ops.p2p_sum_cast(dbuf.peers, d_off + rank * n_q * 4, dq, my_flags, pm.SLOT_BWD_DQ, e)   # each owner sums its block
         return dq, dk, dv
-    elif _schedule(schedule) == "gather":
+    elif sched == "gather":
         gbuf = get_slabs("g_bwd_in", W * (2 * n_q * es + 2 * n_r * 4), dev, 1)[0]
         q_all = _carve(gbuf, 0, (W, B, Hq, Sq, D), dt)
         do_all = _carve(gbuf, W * n_q * es, (W, B, Hq, Sq, D), dt)

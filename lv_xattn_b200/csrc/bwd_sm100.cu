@@ -1,38 +1,39 @@
 // Backward flash-attention block for sm_100a.
 //
 // A CTA owns one 128-row K/V tile of one (batch, kv head) and walks over the packed query rows of the
-// group (g*Sq rows, 128 at a time). Everything is computed in the transposed frame, so that the softmax
-// statistics are per column and no row reduction is needed:
+// group (g*Sq rows of every query block, 128 at a time). Everything is computed in the transposed frame, so
+// that the softmax statistics are per column and no row reduction is needed:
 //     S^T  = K Q^T            (smem x smem)       P^T  = exp2(S^T*c - lse[col])
 //     dP^T = V dO^T           (smem x smem)       dS^T = P^T o (dP^T - delta[col])
 //     dV  += P^T  dO          (TMEM x smem, dO consumed MN-major)
-//     dK  += dS^T Q           (TMEM x smem, Q  consumed MN-major)
-//     dQ^T = K^T dS^T         (smem x smem, both MN-major; dS^T staged through shared memory)
-// dK/dV stay in TMEM for the whole walk (summing over the query heads of the group on the way) and are
-// written once; dQ^T tiles are reduce-added (red.global.add.f32) into the fp32 dQ accumulator. The
-// softmax scale is applied once on the way out (dK, dQ).
+//     dK  += dS^T Q           (smem x smem: dS^T read K-major, Q consumed MN-major)
+//     dQ^T = K^T dS^T         (smem x smem, both MN-major)
+// dK/dV stay in TMEM for the whole walk (summing over the query heads of the group and over the query blocks on
+// the way) and are written once; dQ^T tiles are reduce-added (red.global.add.f32) into the fp32 dQ accumulator.
+// The softmax scale is applied once on the way out (dK, dQ).
 //
-// Every tcgen05.mma is 128 x 128 x 16: on this part an MMA instruction occupies the tensor pipe for about
-// 70 cycles or more whatever its N, so 64-wide query tiles (which would leave TMEM room for double
-// buffering) run the pipe at half efficiency. With 128-wide tiles the 512 TMEM columns are exactly
+// Every tcgen05.mma is 128 x 128 x 16 (64 cycles of tensor pipe; an N = 64 instruction takes 48, so 64-wide query
+// tiles, which would leave TMEM room for double buffering, run the pipe at two thirds). With 128-wide tiles the
+// 512 TMEM columns are exactly
 //     dK [0,128)  dV [128,256)  X [256,384)  Y [384,512)
 //     X: S^T (fp32)  ->  P^T (16-bit, 64 columns)                  Y: dP^T (fp32)  ->  dQ^T (fp32)
 // dS^T lives in shared memory only: it is the B operand of dQ^T (read MN-major) and the A operand of dK (the
-// same bytes read K-major), which frees X as soon as dV has consumed P^T.
-// so the MMA work of a tile is issued as one run (dQ^T, dV, dK of tile j, then S^T, dP^T of tile j+1). What keeps
-// the tensor pipe fed is that nothing else sits on that critical path:
-//   * the P^T half of the elementwise work (the exp) starts as soon as S^T of the next tile is complete, i.e.
-//     while dP^T is still in the pipe; only the dS^T half waits for dP^T;
-//   * the dQ^T tile is taken out of TMEM and reduce-added by four dedicated drain warps. The reduce traffic
-//     (64 KB per tile) moves at ~21 B/clk/SM, about as long as the whole MMA run, so it must not be issued by
-//     the warps that produce P^T/dS^T.
+// same bytes read K-major), which frees X as soon as dV has consumed P^T. The issue order per tile is
+// dV(j), S^T(j+1), dQ^T(j), dK(j), dP^T(j+1). What keeps the tensor pipe fed is that little else sits on the
+// critical path:
+//   * the P^T half of the elementwise work (the exp) starts as soon as S^T of the tile is complete, i.e. while
+//     dP^T is still in the pipe; only the dS^T half waits for dP^T;
+//   * the dQ^T tile is taken out of TMEM and reduce-added by eight dedicated drain warps. The reduce traffic
+//     (64 KB per tile) is what bounds the kernel: with all SMs adding into L2 it moves at ~14 B/clk/SM, about
+//     4,800 cycles per tile against 2,560 cycles of MMA work, so it must not be issued by the warps that
+//     produce P^T/dS^T.
 //
 // CTA anatomy (832 threads, 72 registers each)
 //   warps 0-15  compute: warp w works on K/V rows 32*(w%4).. (its TMEM lane quarter) and query columns
 //               32*(w/4)..; they also write dK/dV at the end
 //   warps 16-23 dQ drain: warp w takes lane quarter w%4 of dQ^T (rows = head dim) and 64 of its query columns,
 //               all loaded at once so that Y is free again right away (a warp sustains about one reduce-add
-//               per 60 cycles, so eight warps are needed to keep up with one tile per ~4,000 cycles)
+//               per 60-75 cycles, so eight warps are needed)
 //   warp  24    TMA producer: K,V once; Q,dO tiles through a 2-stage ring
 //   warp  25    tcgen05.mma issuer; owns the TMEM allocation
 #include "lvx_internal.h"

@@ -306,7 +306,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(args.config, cfg), "l2": "256 MB buffer written between timed steps",
-                       "schedule": "single GPU" if world == 1 else os.environ.get("LVX_SCHEDULE", "gather"),
+                       "schedule": "single GPU" if world == 1 else lvx.attn._schedule(None, q),
                        "timing": "CUDA events per step on the launch stream, summed; max over ranks"},
             "ms_per_layer": ms_per_step, "tflops_per_gpu": value / world,
             "frac_of_tensor_roofline": (roof_job * 1e3) / ms_per_step, "wall_ms": wall_ms,

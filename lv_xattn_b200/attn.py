@@ -44,11 +44,12 @@ from .async_communication import (
 _SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
 
 
-_DEFAULT_SCHEDULE = "gather"
+_DEFAULT_SCHEDULE = "auto"
 
 
 def _schedule(schedule, like=None):
-    """"gather" (default): every rank fetches all W query blocks, makes ONE pass over its K/V shard and the
+    """"auto" (default): "p2p" when every rank of the group can map its peers' memory, else "gather".
+    "gather": every rank fetches all W query blocks, makes ONE pass over its K/V shard and the
     partial results are exchanged and reduced at home -- one kernel launch per pass, dK/dV written once.
     "ring": the reference's step loop, one query block per step with travelling accumulators
     (lv_xattn/attn.py:364-429). "p2p": the "gather" schedule with every exchange done by the library's own
@@ -256,10 +257,12 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl)
         ops.add_cast(dq_acc, None, dt, out=dq)
         return dq, dk, dv
-    elif sched == "p2p":
-        from . import peer_memory as pm
-        if (n_r * 4) % 16:
+    if sched == "p2p" and (n_r * 4) % 16:
+        if (schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)) == "p2p":
             raise ValueError("the p2p schedule needs B*Hq*Sq to be a multiple of 4")
+        sched = "gather"          # picked by "auto": the pull kernels copy 16 bytes at a time
+    if sched == "p2p":
+        from . import peer_memory as pm
         rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
         e = pm.next_epoch(pm.SLOT_BWD_IN)

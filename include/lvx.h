@@ -186,6 +186,27 @@ int lvx_p2p_fwd_merge(const lvx_shape* s, const lvx_peers* parts, size_t o_offse
 int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_dtype, size_t n,
                      const uint32_t* my_flags, int slot, uint32_t epoch, void* stream);
 
+/* Push form of the same exchanges (stores over NVLink are posted, loads are round trips): one launch copies up to
+ * LVX_P2P_MAX_SEGMENTS local segments into every rank's buffer and then publishes `epoch` for `slot` (after a
+ * system-scope fence and a last-block count, inside the same kernel). For destination rank s a segment copies
+ * `bytes` from src + s*src_stride (src_stride 0: the same block to everyone = all-gather; else block s to rank s =
+ * all-to-all) to dst->ptr[s] + dst_offset + rank*dst_rank_stride. The consumer calls lvx_p2p_wait (a one-block
+ * kernel with the bounded wait described above) and then runs the ordinary kernels on its own buffer:
+ * lvx_fwd_block / lvx_bwd_block on gathered blocks, lvx_fwd_merge_parts / lvx_sum_cast on received partials.
+ * Replaces send_recv_fwd_q, send_recv_fwd_Lo, send_recv_bwd_comp, send_recv_bwd_dq + wait_async_handles
+ * (lv_xattn/async_communication.py:138-233, :301-305). */
+#define LVX_P2P_MAX_SEGMENTS 4
+typedef struct lvx_push_segment {
+  const void* src;
+  size_t src_stride;
+  size_t dst_offset;
+  size_t dst_rank_stride;
+  size_t bytes;
+} lvx_push_segment;
+int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
+                 uint32_t epoch, void* stream);
+int lvx_p2p_wait(const uint32_t* my_flags, int world, int slot, uint32_t epoch, void* stream);
+
 /* Self-test of the tensor-core building blocks (TMA tile load, shared-memory and TMEM operand
  * descriptors, TMEM load/store): runs one 128 x N x K product in the operand arrangement `mode`
  * and writes D (fp32 [128,N]) to `d_out`. a/b are device buffers in the arrangement the mode

@@ -21,7 +21,7 @@ SYMBOLS = [
     "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_query_workspace", "lvx_fwd_block",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
     "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
-    "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast",
+    "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast", "lvx_p2p_push", "lvx_p2p_wait",
 ]
 MAX_PEERS = 16      # LVX_MAX_PEERS
 P2P_SLOTS = 8       # LVX_P2P_SLOTS
@@ -33,6 +33,11 @@ class LvxShape(ctypes.Structure):
 
 class LvxPeers(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("ptr", ctypes.c_void_p * 16)]
+
+
+class LvxPushSegment(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("src_stride", ctypes.c_size_t), ("dst_offset", ctypes.c_size_t),
+                ("dst_rank_stride", ctypes.c_size_t), ("bytes", ctypes.c_size_t)]
 
 
 class LvxError(RuntimeError):

@@ -45,6 +45,7 @@ _SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
 
 
 _DEFAULT_SCHEDULE = "auto"
+_AUTO_PEER_SCHEDULE = "p2p_pull"     # the peer-memory form "auto" picks
 
 
 def _schedule(schedule, like=None):
@@ -54,7 +55,8 @@ def _schedule(schedule, like=None):
     "ring": the reference's step loop, one query block per step with travelling accumulators
     (lv_xattn/attn.py:364-429). "p2p": the "gather" schedule with every exchange done by the library's own
     kernels over peer-mapped memory instead of NCCL calls (peer_memory.py; CUDA devices of one NVLink domain
-    only). All move the same bytes per GPU; LVX_SCHEDULE overrides the default."""
+    only): producers store their blocks into the consumers' buffers. "p2p_pull": the same with consumers loading
+    from the producers' buffers (slower: loads over NVLink are round trips). All move the same bytes per GPU; LVX_SCHEDULE overrides the default."""
     s = schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)
     if s == "auto":
         # p2p where every rank can map its peers' memory (decided once, collectively), NCCL collectives otherwise
@@ -62,8 +64,8 @@ def _schedule(schedule, like=None):
         if like is not None and like.is_cuda and get_sequence_parallel_size() > 1:
             from .peer_memory import peer_memory_available
             if peer_memory_available(like.device):
-                s = "p2p"
-    if s not in ("gather", "ring", "p2p"):
+                s = _AUTO_PEER_SCHEDULE
+    if s not in ("gather", "ring", "p2p", "p2p_pull"):
         raise ValueError(f"unknown schedule {s!r}")
     return s
 
@@ -136,7 +138,38 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
 
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
     sched = _schedule(schedule, q)
+    if sched in ("p2p", "p2p_pull") and (n_l * 4) % 16:
+        if (schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)) != "auto":
+            raise ValueError("the p2p schedules need B*Hq*Sq to be a multiple of 4")
+        sched = "gather"          # picked by "auto": the exchange kernels copy 16 bytes at a time
     if sched == "p2p":
+        from . import peer_memory as pm
+        flag_peers, my_flags = pm.get_flags(dev)
+        # every rank stores its Q block into all ranks' gathered buffer (posted NVLink stores) and signals
+        e = pm.next_epoch(pm.SLOT_FWD_Q)
+        qbuf = pm.get_peer_buffer("p2p_q_all", 2 * W * n_o * es, dev)
+        q_off = (e & 1) * W * n_o * es
+        ops.p2p_push(qbuf.peers, flag_peers, [(qc, False, q_off, n_o * es)], pm.SLOT_FWD_Q, e)
+        ops.p2p_wait(my_flags, W, pm.SLOT_FWD_Q, e)
+        q_all = _carve(qbuf.local, q_off, (W, B, Hq, Sq, D), dt)
+        part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl)
+        sbuf = get_slabs("g_acc_send", W * (n_o + n_l) * 4, dev, 1)[0]
+        o_parts = _carve(sbuf, 0, (W, B, Hq, Sq, D), torch.float32)
+        l_parts = _carve(sbuf, W * n_o * 4, (W * B * Hq, Sq), torch.float32)
+        ops.fwd_combine(part, None, None, o_parts, l_parts, False)
+        # partial (O, lse) of block s goes to rank s; the owner merges what it received
+        e = pm.next_epoch(pm.SLOT_FWD_PARTS)
+        blk = W * (n_o + n_l) * 4
+        pbuf = pm.get_peer_buffer("p2p_parts_recv", 2 * blk, dev)
+        p_off = (e & 1) * blk
+        ops.p2p_push(pbuf.peers, flag_peers, [(o_parts, True, p_off, n_o * 4), (l_parts, True, p_off + W * n_o * 4, n_l * 4)],
+                     pm.SLOT_FWD_PARTS, e)
+        ops.p2p_wait(my_flags, W, pm.SLOT_FWD_PARTS, e)
+        o_recv = _carve(pbuf.local, p_off, (W, B, Hq, Sq, D), torch.float32)
+        l_recv = _carve(pbuf.local, p_off + W * n_o * 4, (W, B * Hq, Sq), torch.float32)
+        ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
+        return q, k, v, o, L
+    if sched == "p2p_pull":
         from . import peer_memory as pm
         rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
@@ -257,11 +290,39 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl)
         ops.add_cast(dq_acc, None, dt, out=dq)
         return dq, dk, dv
-    if sched == "p2p" and (n_r * 4) % 16:
-        if (schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)) == "p2p":
-            raise ValueError("the p2p schedule needs B*Hq*Sq to be a multiple of 4")
-        sched = "gather"          # picked by "auto": the pull kernels copy 16 bytes at a time
+    if sched in ("p2p", "p2p_pull") and (n_r * 4) % 16:
+        if (schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)) != "auto":
+            raise ValueError("the p2p schedules need B*Hq*Sq to be a multiple of 4")
+        sched = "gather"          # picked by "auto": the exchange kernels copy 16 bytes at a time
     if sched == "p2p":
+        from . import peer_memory as pm
+        flag_peers, my_flags = pm.get_flags(dev)
+        e = pm.next_epoch(pm.SLOT_BWD_IN)
+        blk = W * (2 * n_q * es + 2 * n_r * 4)
+        ibuf = pm.get_peer_buffer("p2p_bwd_all", 2 * blk, dev)
+        base = (e & 1) * blk
+        offs = (base, base + W * n_q * es, base + 2 * W * n_q * es, base + 2 * W * n_q * es + W * n_r * 4)
+        ops.p2p_push(ibuf.peers, flag_peers, [(qc, False, offs[0], n_q * es), (doc, False, offs[1], n_q * es),
+                                              (Lc, False, offs[2], n_r * 4), (delta, False, offs[3], n_r * 4)],
+                     pm.SLOT_BWD_IN, e)
+        ops.p2p_wait(my_flags, W, pm.SLOT_BWD_IN, e)
+        q_all = _carve(ibuf.local, offs[0], (W, B, Hq, Sq, D), dt)
+        do_all = _carve(ibuf.local, offs[1], (W, B, Hq, Sq, D), dt)
+        l_all = _carve(ibuf.local, offs[2], (W * B * Hq, Sq), torch.float32)
+        d_all = _carve(ibuf.local, offs[3], (W * B * Hq, Sq), torch.float32)
+        dq_parts = _carve(get_slabs("g_dq_send", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
+        dq_parts.zero_()
+        dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        ops.bwd_block(q_all, do_all, l_all, d_all, kc, vc, sm_scale, dq_parts, dk, dv, "final", kvl)
+        e = pm.next_epoch(pm.SLOT_BWD_DQ)
+        dbuf = pm.get_peer_buffer("p2p_dq_recv", 2 * W * n_q * 4, dev)
+        d_off = (e & 1) * W * n_q * 4
+        ops.p2p_push(dbuf.peers, flag_peers, [(dq_parts, True, d_off, n_q * 4)], pm.SLOT_BWD_DQ, e)
+        ops.p2p_wait(my_flags, W, pm.SLOT_BWD_DQ, e)
+        ops.sum_cast(_carve(dbuf.local, d_off, (W, B, Hq, Sq, D), torch.float32), dt, out=dq)
+        return dq, dk, dv
+    elif sched == "p2p_pull":
         from . import peer_memory as pm
         rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)

@@ -13,6 +13,12 @@
 // A buffer may be rewritten two epochs later: by then every peer has signalled the epoch in between, which it
 // does only after its pull of the earlier epoch has finished (stream order). Callers therefore alternate two
 // buffers per slot. Only plain loads and stores touch peer memory (no TMA, no multicast).
+//
+// The push form (p2p_push_kernel + p2p_wait_kernel) turns the direction round: the producer stores its blocks into
+// the consumers' buffers and publishes the epoch from the same kernel, after a system-scope fence by every thread
+// and a last-block-done count; the consumer runs a one-block wait and then works on local memory with the ordinary
+// kernels. Same flag words, same two-buffer rule (the consumer has read a buffer before it signals the epoch
+// after, and the producer has waited for that signal before it stores into the buffer again).
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
 #include <cuda_bf16.h>
@@ -165,6 +171,59 @@ p2p_sum_cast_kernel(PeerPtrs parts, size_t offset, int world, void* __restrict__
   }
 }
 
+// ---- push form: the producer stores into the consumers' memory, the consumer only waits -----------------
+// Stores over NVLink are posted, loads are round trips: pushing moves the same bytes in less time than pulling.
+struct PushSeg {
+  const uint8_t* src;       // local source
+  size_t src_stride;        // 0: the same bytes go to every rank (all-gather); else block s goes to rank s (all-to-all)
+  size_t dst_offset;        // byte offset inside the peers' buffer
+  size_t dst_rank_stride;   // this rank's data lands at dst_offset + rank * dst_rank_stride
+  size_t bytes;             // per destination, multiple of 16
+};
+struct PushArgs {
+  PushSeg seg[LVX_P2P_MAX_SEGMENTS];
+  int nseg;
+};
+
+__device__ unsigned int g_push_done[LVX_P2P_SLOTS];
+
+// Every block copies its share of every (segment, destination) pair; each thread fences its stores at system
+// scope; the block that finishes last publishes the epoch to every rank, so the flag can never overtake the data.
+__global__ void __launch_bounds__(256)
+p2p_push_kernel(PeerPtrs dst, PeerPtrs flags, PushArgs a, int world, int rank, int slot, uint32_t epoch) {
+  const size_t gstride = size_t(gridDim.x) * blockDim.x;
+  const size_t gtid = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (int g = 0; g < a.nseg; ++g) {
+    const PushSeg sg = a.seg[g];
+    const size_t n16 = sg.bytes >> 4;
+    const size_t total = n16 * world;
+    for (size_t i = gtid; i < total; i += gstride) {
+      const int s = int(i / n16);
+      const size_t off = (i - size_t(s) * n16) << 4;
+      const float4 v = *reinterpret_cast<const float4*>(sg.src + size_t(s) * sg.src_stride + off);
+      uint8_t* d = const_cast<uint8_t*>(dst.p[s]) + sg.dst_offset + size_t(rank) * sg.dst_rank_stride + off;
+      *reinterpret_cast<float4*>(d) = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(&g_push_done[slot], 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) g_push_done[slot] = 0;     // launches on one slot are stream-ordered
+    if (threadIdx.x < world) {
+      __threadfence_system();
+      uint32_t* f = reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(flags.p[threadIdx.x])) + slot * LVX_MAX_PEERS + rank;
+      st_release_sys(f, epoch);
+    }
+  }
+}
+
+__global__ void p2p_wait_kernel(const uint32_t* my_flags, int world, int slot, uint32_t epoch, int* status) {
+  p2p_wait_all(my_flags, world, slot, epoch, status);
+}
+
 static int peers_ok(const lvx_peers* p, const char* who) {
   if (!p) return fail(LVX_ERR_NULL, "%s: null peer table", who);
   if (p->world < 1 || p->world > LVX_MAX_PEERS || p->rank < 0 || p->rank >= p->world)
@@ -265,6 +324,49 @@ int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_d
   if (out_dtype == LVX_BF16) p2p_sum_cast_kernel<0><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status);
   else if (out_dtype == LVX_FP16) p2p_sum_cast_kernel<1><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status);
   else p2p_sum_cast_kernel<2><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
+}
+
+int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
+                 uint32_t epoch, void* stream) {
+  const char* who = "lvx_p2p_push";
+  int rc = peers_ok(dst, who);
+  if (rc) return rc;
+  if ((rc = peers_ok(flags, who))) return rc;
+  if (flags->world != dst->world || flags->rank != dst->rank) return fail(LVX_ERR_SHAPE, "%s: the two peer tables disagree", who);
+  if (!segments || nseg < 1 || nseg > LVX_P2P_MAX_SEGMENTS) return fail(LVX_ERR_SHAPE, "%s: 1..%d segments", who, LVX_P2P_MAX_SEGMENTS);
+  if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  PushArgs a;
+  a.nseg = nseg;
+  size_t most = 0;
+  for (int g = 0; g < nseg; ++g) {
+    const lvx_push_segment& u = segments[g];
+    if (!u.src) return fail(LVX_ERR_NULL, "%s: segment %d has no source", who, g);
+    if ((reinterpret_cast<uintptr_t>(u.src) & 15u) || (u.src_stride & 15u) || (u.dst_offset & 15u) || (u.dst_rank_stride & 15u) ||
+        (u.bytes & 15u))
+      return fail(LVX_ERR_ALIGN, "%s: segment %d: addresses, strides and sizes must be multiples of 16 bytes", who, g);
+    a.seg[g].src = static_cast<const uint8_t*>(u.src);
+    a.seg[g].src_stride = u.src_stride;
+    a.seg[g].dst_offset = u.dst_offset;
+    a.seg[g].dst_rank_stride = u.dst_rank_stride;
+    a.seg[g].bytes = u.bytes;
+    if (u.bytes > most) most = u.bytes;
+  }
+  p2p_push_kernel<<<grid_for((most >> 4) * dst->world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      to_dev(dst), to_dev(flags), a, dst->world, dst->rank, slot, epoch);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
+}
+
+int lvx_p2p_wait(const uint32_t* my_flags, int world, int slot, uint32_t epoch, void* stream) {
+  const char* who = "lvx_p2p_wait";
+  if (!my_flags) return fail(LVX_ERR_NULL, "%s: null flag array", who);
+  if (world < 1 || world > LVX_MAX_PEERS) return fail(LVX_ERR_SHAPE, "%s: world %d out of range", who, world);
+  if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  int* status = device_status_ptr();
+  if (!status) return fail(LVX_ERR_DRIVER, "%s: no device status word", who);
+  p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, world, slot, epoch, status);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
 }

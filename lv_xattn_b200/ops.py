@@ -282,6 +282,39 @@ def p2p_sum_cast(parts_peers, offset: int, out, my_flags, slot: int, epoch: int)
     _count()
 
 
+def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int):
+    """One launch: for every rank s and every segment (src tensor, all_to_all, dst_offset, dst_rank_stride),
+    copies src (all_to_all False: the whole tensor to everyone; True: its block s, src being [W, ...]) into rank
+    s's buffer at dst_offset + rank*dst_rank_stride, then publishes `epoch` for `slot` to every rank."""
+    lib = _lib.load()
+    W = dst_peers.world
+    arr = (_lib.LvxPushSegment * len(segments))()
+    keep = []
+    for i, (src, a2a, dst_offset, dst_rank_stride) in enumerate(segments):
+        _require_cuda(src)
+        src = _contig(src)
+        keep.append(src)
+        total = src.numel() * src.element_size()
+        nbytes = total // W if a2a else total
+        arr[i].src = src.data_ptr()
+        arr[i].src_stride = nbytes if a2a else 0
+        arr[i].dst_offset = dst_offset
+        arr[i].dst_rank_stride = dst_rank_stride
+        arr[i].bytes = nbytes
+    _lib.check(lib.lvx_p2p_push(ctypes.byref(dst_peers), ctypes.byref(flags_peers), arr, len(segments), slot,
+                                ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()), "lvx_p2p_push")
+    _count()
+
+
+def p2p_wait(my_flags, world: int, slot: int, epoch: int):
+    """Orders the current stream after every rank's push of `epoch` on `slot` (bounded wait on the device)."""
+    _require_cuda(my_flags)
+    lib = _lib.load()
+    _lib.check(lib.lvx_p2p_wait(_lib.ptr(my_flags), world, slot, ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()),
+               "lvx_p2p_wait")
+    _count()
+
+
 def add_cast(a, b, out_dtype, out=None):
     """cast(a + b) for fp32 a (and optional fp32 b of the same shape); written into `out` when given."""
     _require_cuda(a, b)

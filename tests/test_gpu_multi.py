@@ -30,6 +30,6 @@ def test_ring_nccl(world):
 
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_memory_schedule(world):
-    """The exchanges done by the library's own kernels over peer-mapped memory, twice in a row (both buffers of
-    every slot), against the NCCL schedule and the oracle."""
-    _run(world, "gather,p2p,p2p,p2p", 29650 + world)
+    """The exchanges done by the library's own kernels over peer-mapped memory (push form three times in a row,
+    so that both buffers of every slot are reused; then the pull form), against the NCCL schedule and the oracle."""
+    _run(world, "gather,p2p,p2p,p2p,p2p_pull,p2p_pull", 29650 + world)

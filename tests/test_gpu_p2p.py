@@ -77,6 +77,32 @@ def test_gather_merge_sum(dev, world):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("world", [1, 3, 8])
+def test_push_all_gather_and_all_to_all(dev, world):
+    """lvx_p2p_push / lvx_p2p_wait with emulated ranks: an all-gather segment and an all-to-all segment in one
+    launch per rank, two epochs (both halves of a double buffer)."""
+    from lv_xattn_b200 import _lib, ops
+    torch.manual_seed(10 + world)
+    n = 4096                                      # floats per block
+    flags = [torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=dev) for _ in range(world)]
+    recv = [torch.zeros(2, 2, world, n, device=dev) for _ in range(world)]          # [parity][segment][from][n]
+    for epoch in (1, 2, 3):
+        par = epoch & 1
+        own = [torch.randn(n, device=dev) for _ in range(world)]                      # gathered by everyone
+        parts = [torch.randn(world, n, device=dev) for _ in range(world)]             # block s goes to rank s
+        for r in range(world):
+            base = par * 2 * world * n * 4
+            ops.p2p_push(_peers(recv, r), _peers(flags, r),
+                         [(own[r], False, base, n * 4), (parts[r], True, base + world * n * 4, n * 4)], 5, epoch)
+        for r in range(world):
+            ops.p2p_wait(flags[r], world, 5, epoch)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(recv[r][par, 0], torch.stack(own))
+            assert torch.equal(recv[r][par, 1], torch.stack([parts[c][r] for c in range(world)]))
+    assert _lib.device_status() == 0
+
+
 def test_argument_checks(dev):
     from lv_xattn_b200 import _lib, ops
     flags = torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=dev)

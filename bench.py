@@ -168,6 +168,7 @@ def main():
     ap.add_argument("--config", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="K/V chunks of the host-streamed end-to-end step")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.impl == "reference":
@@ -280,7 +281,7 @@ def main():
         ho, hdq = torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory()
         hdk, hdv = torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()
 
-        streamer = lvx.HostStreamedAttention(dev, chunks=8)
+        streamer = lvx.HostStreamedAttention(dev, chunks=args.e2e_chunks)
 
         def step_e2e():
             streamer.step(hq, hk, hv, hdo, scale, ho, hdq, hdk, hdv)

@@ -101,11 +101,12 @@ struct BwdParams {
   int* status;
 };
 
-// Development aid (LVX_BWD_DEBUG bit 128): cycle stamps of CTA (0,0), tiles 4..11, 16 slots per tile and role.
+// Development aid, compiled into a separate instantiation that runs only when LVX_BWD_DEBUG is set (bit 128:
+// cycle stamps of CTA (0,0), tiles 4..11, 16 slots per tile and role; bit 1: the dQ reduce-adds are skipped).
 __device__ long long g_bwd_ts[2 * 8 * 16];
 #define BWD_TS(role, slot)                                                                         \
   do {                                                                                             \
-    if ((p.debug & 128) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && j >= 4 && j < 12)    \
+    if (DBG && (p.debug & 128) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && j >= 4 && j < 12)    \
       g_bwd_ts[((role) * 8 + (j - 4)) * 16 + (slot)] = clock64();                                  \
   } while (0)
 
@@ -117,7 +118,7 @@ __device__ __forceinline__ float2 unpack16x2(uint32_t v) {
   return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
-template <bool IS_BF16>
+template <bool IS_BF16, bool DBG>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
            const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
@@ -362,7 +363,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);     // Y is free for the next tile's dP^T
         if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 6);
-        if (!(p.debug & 1)) {
+        if (!DBG || !(p.debug & 1)) {
           const int row0 = (j % nq) * 128 + ch * 64;
           const int ncols = min(64, p.rows - row0);
           float* dst = p.dq_acc + (size_t(slab + (j / nq) * p.kv_slabs) * p.rows + row0) * 128 + d;
@@ -576,16 +577,19 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   }
 
   dim3 grid((s.Skv + 127) / 128, s.B * s.Hkv, 1);
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kern) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e == cudaSuccess) kern<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tmQ, tmDO, tmK, tmV, p);
+  };
   if (s.dtype == LVX_BF16) {
-    e = cudaFuncSetAttribute(bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(bwd)");
-    bwd_kernel<true><<<grid, BWD_THREADS, BWD_SMEM, st>>>(tmQ, tmDO, tmK, tmV, p);
+    if (p.debug) go(bwd_kernel<true, true>);
+    else go(bwd_kernel<true, false>);
   } else {
-    e = cudaFuncSetAttribute(bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(bwd)");
-    bwd_kernel<false><<<grid, BWD_THREADS, BWD_SMEM, st>>>(tmQ, tmDO, tmK, tmV, p);
+    if (p.debug) go(bwd_kernel<false, true>);
+    else go(bwd_kernel<false, false>);
   }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(bwd)");
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "bwd_kernel launch");
   if (p.debug & 128) {

@@ -63,16 +63,17 @@ struct FwdParams {
 };
 
 // Development aid (LVX_FWD_DEBUG=1): cycle stamps of CTA (0,0,0), K/V tiles 4..11, 8 slots per tile and role.
+// The stamped kernel is a separate instantiation: even the untaken test costs the lone softmax warps ~2 %.
 __device__ long long g_fwd_ts[3 * 8 * 8];
 #define FWD_TS(role, slot)                                                                              \
   do {                                                                                                  \
-    if (p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && j >= 4 && j < 12) \
+    if (STAMPS && p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && j >= 4 && j < 12) \
       g_fwd_ts[((role) * 8 + (j - 4)) * 8 + (slot)] = clock64();                                        \
   } while (0)
 
 #define FWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x100 | ((role) << 5) | (bar))
 
-template <bool IS_BF16>
+template <bool IS_BF16, bool STAMPS>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -528,8 +529,13 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
     if (e == cudaSuccess) kern<<<grid, FWD_THREADS, FWD_SMEM, st>>>(tmQ, tmK, tmV, p);
   };
-  if (s.dtype == LVX_BF16) go(fwd_kernel<true>);
-  else go(fwd_kernel<false>);
+  if (s.dtype == LVX_BF16) {
+    if (p.debug) go(fwd_kernel<true, true>);
+    else go(fwd_kernel<true, false>);
+  } else {
+    if (p.debug) go(fwd_kernel<false, true>);
+    else go(fwd_kernel<false, false>);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fwd)");
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_kernel launch");

@@ -6,7 +6,10 @@ import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 import torch  # noqa: E402
+
+import _parity  # noqa: E402
 
 import lv_xattn_b200 as lvx  # noqa: E402
 from lv_xattn_b200 import _lib  # noqa: E402
@@ -34,22 +37,26 @@ for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
                                         schedule=sched)
         if rep == 0:
             first = [t.clone() for t in (o, L, dq, dk, dv)]
-        for a, b in zip(first, (o, L, dq, dk, dv)):      # every schedule computes the same thing
-            assert (a.float() - b.float()).abs().max().item() <= (1e-4 if dtype == torch.float32 else 2e-2), sched
+        for name, a, b in zip(("o", "lse", "dq", "dk", "dv"), first, (o, L, dq, dk, dv)):   # every schedule computes the same thing
+            if name == "lse":
+                _parity.assert_lse_close(b.cpu(), a.cpu(), f"{sched}_vs_{schedules[0]}", 1e-4)
+            elif dtype == torch.float32:
+                _parity.assert_fp32(b.cpu(), a.cpu(), name, f"{sched}_vs_{schedules[0]}")
+            else:
+                _parity.assert_close(b.float().cpu(), a.float().cpu(), name, f"{sched}_vs_{schedules[0]}", *_parity.BF16[name])
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     Sl = Sq // world
     lse_l = orc.shard(lse_ref.unsqueeze(-1), rank, world).squeeze(-1)
-    errs = {
-        "o": (o.float().cpu() - orc.shard(o_ref, rank, world)).abs().max().item(),
-        "lse": (L.cpu().view(B, Hq, Sl) - lse_l).abs().max().item(),
-        "dq": (dq.float().cpu() - orc.shard(dq_ref, rank, world)).abs().max().item(),
-        "dk": (dk.float().cpu() - orc.shard(dk_ref, rank, world)).abs().max().item(),
-        "dv": (dv.float().cpu() - orc.shard(dv_ref, rank, world)).abs().max().item(),
-    }
-    if dtype == torch.float32:
-        assert all(e <= 1e-4 for e in errs.values()), (rank, errs)
-    else:
-        assert errs["lse"] <= 1e-3 and all(errs[n] <= 2e-2 for n in ("o", "dq", "dk", "dv")), (rank, errs)
+    label = f"w{world}_r{rank}_{dtype}"
+    got = {"o": o.float().cpu(), "dq": dq.float().cpu(), "dk": dk.float().cpu(), "dv": dv.float().cpu()}
+    ref = {"o": orc.shard(o_ref, rank, world), "dq": orc.shard(dq_ref, rank, world),
+           "dk": orc.shard(dk_ref, rank, world), "dv": orc.shard(dv_ref, rank, world)}
+    _parity.assert_lse_close(L.cpu().view(B, Hq, Sl), lse_l, label, 1e-4 if dtype == torch.float32 else 1e-3)
+    for name in got:
+        if dtype == torch.float32:
+            _parity.assert_fp32(got[name], ref[name], name, label)
+        else:
+            _parity.assert_close(got[name], ref[name], name, label, *_parity.BF16[name])
 print(f"RANK_OK {rank}", flush=True)
 torch.distributed.destroy_process_group()

@@ -6,6 +6,8 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+if os.path.join(ROOT, "tests") not in sys.path:
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 def pytest_configure(config):
@@ -18,3 +20,12 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda", 0)
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With LVX_PARITY_LOG set, every parity comparison's measured errors are appended to that file."""
+    try:
+        import _parity
+    except ImportError:
+        from tests import _parity
+    _parity.dump_measured()

@@ -5,7 +5,10 @@ interpreter, its own step loop and P2P layer over gloo CPU ranks) on seeded inpu
 benchmark's protocol (test.py:101-107) and sharded as test.py:164-178. Only runs where the reference checkout
 is present; the fixtures it writes are committed and are what tests/test_oracle.py reads.
 
+    python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 1
     python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 2
+    python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 4 --seed 2 --heads 1 \
+        --sq-per-rank 32 --skv-per-rank 512 --tag _skv2048_seed2
 
 Three shims touch no reference file: the process group is created with gloo before
 `lv_xattn.initialize_distributed()` (which then skips its NCCL init, async_communication.py:39-45),
@@ -20,7 +23,7 @@ import sys
 import numpy as np
 
 
-def worker(rank, world, ref, port, out_dir):
+def worker(rank, world, ref, port, out_dir, seed=1, heads=2, sq_per_rank=32, skv_per_rank=128, tag=""):
     os.environ.update(TRITON_INTERPRET="1", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                       WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
     sys.dont_write_bytecode = True
@@ -35,9 +38,9 @@ def worker(rank, world, ref, port, out_dir):
     from lv_xattn import flash_attn_kernels as fk
     fk._bwd_kernel.configs = fk._bwd_kernel.configs[0:1]
 
-    B, H, D = 1, 2, 128
-    Sq, Skv = 32 * world, 128 * world
-    torch.manual_seed(1)                                         # test.py:101
+    B, H, D = 1, heads, 128
+    Sq, Skv = sq_per_rank * world, skv_per_rank * world
+    torch.manual_seed(seed)                                      # test.py:101
     q = torch.empty(B, H, Sq, D, dtype=torch.float16).normal_(0.0, 0.5)
     k = torch.empty(B, H, Skv, D, dtype=torch.float16).normal_(0.0, 0.5)
     v = torch.empty(B, H, Skv, D, dtype=torch.float16).normal_(0.0, 0.5)
@@ -59,11 +62,11 @@ def worker(rank, world, ref, port, out_dir):
         dist.all_gather(bufs, t)
         gathered[name] = torch.stack(bufs).numpy()               # [W, ...] per-rank shards
     if rank == 0:
-        np.savez_compressed(os.path.join(out_dir, f"ref_lvxattn_w{world}.npz"),
+        np.savez_compressed(os.path.join(out_dir, f"ref_lvxattn_w{world}{tag}.npz"),
                             q=q.numpy(), k=k.numpy(), v=v.numpy(), do=do.numpy(), scale=np.float32(scale),
                             world=np.int32(world), **{f"ref_{n}": a.astype(np.float16 if n != "L" else np.float32)
                                                       for n, a in gathered.items()})
-        print("wrote", f"ref_lvxattn_w{world}.npz")
+        print("wrote", f"ref_lvxattn_w{world}{tag}.npz")
     dist.destroy_process_group()
 
 
@@ -72,7 +75,13 @@ if __name__ == "__main__":
     ap.add_argument("--ref", required=True, help="path of the reference checkout (uw-mad-dash/LV-XAttn)")
     ap.add_argument("--world", type=int, default=1)
     ap.add_argument("--port", type=int, default=29533)
+    ap.add_argument("--seed", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=2)
+    ap.add_argument("--sq-per-rank", type=int, default=32)
+    ap.add_argument("--skv-per-rank", type=int, default=128)
+    ap.add_argument("--tag", default="", help="suffix of the fixture's file name")
     a = ap.parse_args()
     import torch.multiprocessing as mp
     out = os.path.dirname(os.path.abspath(__file__))
-    mp.spawn(worker, args=(a.world, a.ref, a.port, out), nprocs=a.world, join=True)
+    mp.spawn(worker, args=(a.world, a.ref, a.port, out, a.seed, a.heads, a.sq_per_rank, a.skv_per_rank, a.tag),
+             nprocs=a.world, join=True)

@@ -1,18 +1,26 @@
-"""Size-independent properties at the benchmark's full single-GPU size (B=1, Hq=32, Hkv=8, Sq=2048, Skv=131072,
-bf16), where the CPU oracle is out of reach:
+"""The benchmark's full single-GPU sizes, where the CPU oracle is out of reach.
+
+Checked against the oracle's per-KV-group fp32 form run on the GPU (oracle.group_fwd_bwd: plain fp32 torch
+matmuls, one head at a time -- the torch fp32 reference of the same op): for two KV groups of each shape EVERY
+row of O, lse and dQ of their query heads and EVERY key of dK and dV, under the absolute bars (2e-2, lse 1e-3)
+and the relative ones of tests/_parity.py (at these lengths |O| ~ 7e-3, so only the relative bars can fail).
+Plus size-independent properties:
   * V = 1 everywhere  =>  O = 1 exactly (softmax rows sum to one) and dK = dQ = 0 up to rounding
   * attention over the whole K/V == merge of attention over its two halves (the shard merge identity)
-  * the backward is linear in dO:  grad(a*dO) = a*grad(dO)
-  * a sampled set of query rows against a direct fp32 computation on the GPU (torch fp32 reference of the same op)
+  * the backward is linear in dO:  grad(2*dO) = 2*grad(dO)
 """
 import math
 
 import pytest
 import torch
 
+import _parity
+from oracle import attention_oracle as orc
+
 pytestmark = pytest.mark.gpu
 SCALE = 1.0 / math.sqrt(128.0)
 B, HQ, HKV, SQ, SKV = 1, 32, 8, 2048, 131072
+G = HQ // HKV
 
 
 @pytest.fixture(scope="module")
@@ -25,6 +33,34 @@ def tensors(cuda_device):
     return q, k, v, do
 
 
+def check_groups(label, groups, q, k, v, do, o, L, dq, dk, dv, valid=None):
+    """groups: (batch, kv head) pairs; everything those groups produce against the fp32 group reference."""
+    Bz, Hq, Sq, _ = q.shape
+    L3 = L.view(Bz, Hq, Sq)
+    for b, hk in groups:
+        hs = slice(hk * G, (hk + 1) * G)
+        n = None if valid is None else valid[b]
+        o_r, lse_r, dq_r, dk_r, dv_r = orc.group_fwd_bwd(q[b, hs], k[b, hk], v[b, hk], do[b, hs], SCALE, n)
+        tag = f"{label}_b{b}_kv{hk}"
+        _parity.assert_lse_close(L3[b, hs], lse_r, tag)
+        _parity.assert_close(o[b, hs].float(), o_r, "o", tag, *_parity.BF16["o"])
+        _parity.assert_close(dq[b, hs].float(), dq_r, "dq", tag, *_parity.BF16["dq"])
+        _parity.assert_close(dk[b, hk].float(), dk_r, "dk", tag, *_parity.BF16["dk"])
+        _parity.assert_close(dv[b, hk].float(), dv_r, "dv", tag, *_parity.BF16["dv"])
+
+
+def test_benchmark_shape_against_fp32_reference(tensors):
+    """B=1, Hq=32, Hkv=8, Sq=2048, Skv=131072, bf16: KV groups 0 and 5 in full."""
+    import lv_xattn_b200 as lvx
+    from lv_xattn_b200 import _lib
+    q, k, v, do = tensors
+    _, _, _, o, L = lvx._attn_forward(q, k, v, False, SCALE, None)
+    dq, dk, dv = lvx._attn_backward(do, q, k, v, o, L, False, SCALE, None, "flash")
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    check_groups("config2", [(0, 0), (0, 5)], q, k, v, do, o, L, dq, dk, dv)
+
+
 def test_constant_v_gives_constant_o(tensors):
     import lv_xattn_b200 as lvx
     q, k, v, do = tensors
@@ -32,10 +68,12 @@ def test_constant_v_gives_constant_o(tensors):
     _, _, _, o, L = lvx._attn_forward(q, k, ones, False, SCALE, None)
     assert torch.equal(o, torch.ones_like(o))
     dq, dk, dv = lvx._attn_backward(do, q, k, ones, o, L, False, SCALE, None, "flash")
-    # dP = dO V^T is constant along keys, delta = rowsum(dO), so dS = P*(dP - delta) = 0
-    assert dq.float().abs().max().item() <= 2e-2
-    assert dk.float().abs().max().item() <= 2e-2
-    assert torch.isfinite(dv.float()).all()
+    # dP = dO V^T is constant along keys and equals delta = rowsum(dO), so dS = P*(dP - delta) vanishes up to the
+    # summation order of the two row sums: ~1e-5 * P, far below the ~1e-3 these gradients have for random V
+    assert dq.float().abs().max().item() <= 1e-5
+    assert dk.float().abs().max().item() <= 1e-5
+    # dV[j] = sum_i P[i,j] dO[i]: finite and not identically zero
+    assert torch.isfinite(dv.float()).all() and dv.float().abs().max().item() > 0
 
 
 def test_merge_of_halves_equals_whole(tensors):
@@ -45,7 +83,8 @@ def test_merge_of_halves_equals_whole(tensors):
     o_full, l_full = ops.fwd_block(q, k, v, SCALE)
     o1, l1 = ops.fwd_block(q, k[:, :, :h].contiguous(), v[:, :, :h].contiguous(), SCALE, final=False)
     o2, l2 = ops.fwd_block(q, k[:, :, h:].contiguous(), v[:, :, h:].contiguous(), SCALE, o_in=o1, lse_in=l1)
-    assert (o_full.float() - o2.float()).abs().max().item() <= 4e-3      # one bf16 ulp at |O| ~ 0.02 is 1.2e-4
+    # both sides are rounded to bf16 once: relative Frobenius distance of two roundings of the same value ~1.6e-3
+    _parity.assert_close(o2.float(), o_full.float(), "o", "merge_halves", 4e-3, 5e-3, 2e-2)
     assert (l_full - l2).abs().max().item() <= 1e-4
 
 
@@ -55,29 +94,16 @@ def test_backward_is_linear_in_do(tensors):
     _, _, _, o, L = lvx._attn_forward(q, k, v, False, SCALE, None)
     g1 = lvx._attn_backward(do, q, k, v, o, L, False, SCALE, None, "flash")
     g2 = lvx._attn_backward((do.float() * 2).bfloat16(), q, k, v, o, L, False, SCALE, None, "flash")
-    for a, b in zip(g1, g2):       # scaling by 2 is exact in bf16, so only the final rounding differs
-        assert (a.float() * 2 - b.float()).abs().max().item() <= 1e-2 * max(1.0, b.float().abs().max().item())
-
-
-def test_sampled_rows_against_direct_fp32(tensors):
-    """64 query rows of 4 heads against a direct fp32 softmax(QK^T)V on the GPU."""
-    import lv_xattn_b200 as lvx
-    q, k, v, _ = tensors
-    _, _, _, o, L = lvx._attn_forward(q, k, v, False, SCALE, None)
-    rows = torch.arange(0, SQ, SQ // 64, device=q.device)
-    for h in (0, 5, 18, 31):
-        kh, vh = k[0, h // 4].float(), v[0, h // 4].float()
-        s = (q[0, h, rows].float() @ kh.t()) * SCALE
-        lse = torch.logsumexp(s, -1)
-        ref = torch.softmax(s, -1) @ vh
-        assert (o[0, h, rows].float() - ref).abs().max().item() <= 2e-2
-        assert (L.view(B, HQ, SQ)[0, h, rows] - lse).abs().max().item() <= 1e-3
+    for name, a, b in zip(("dq", "dk", "dv"), g1, g2):   # scaling by 2 is exact in bf16: only the final roundings differ
+        _parity.assert_close(a.float() * 2, b.float(), name, "linear_in_do", 1e-2, 5e-3, 2e-2)
 
 
 def test_long_visual_stress_shape_with_key_padding(cuda_device):
     """The long-visual stress shape on one GPU: B=2, Sq=256, 1,048,576 keys per sample, valid lengths
-    1,048,576 and 786,432. Sampled rows against direct fp32; gradients of padded keys are exactly zero."""
+    1,048,576 and 786,432. KV groups (0, 0) and (1, 7) in full against the fp32 group reference; gradients of
+    padded keys are exactly zero."""
     import lv_xattn_b200 as lvx
+    from lv_xattn_b200 import _lib
     d = cuda_device
     Bz, Sq, Skv = 2, 256, 1048576
     valid = [1048576, 786432]
@@ -88,22 +114,9 @@ def test_long_visual_stress_shape_with_key_padding(cuda_device):
     do = torch.empty(Bz, HQ, Sq, 128, device=d).normal_(0, 1.0, generator=g).bfloat16()
     _, _, _, o, L = lvx._attn_forward(q, k, v, False, SCALE, None, kv_valid_len=valid)
     dq, dk, dv = lvx._attn_backward(do, q, k, v, o, L, False, SCALE, None, "flash", kv_valid_len=valid)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
     assert torch.isfinite(o.float()).all() and torch.isfinite(dq.float()).all()
     assert dk[1, :, valid[1]:].abs().max().item() == 0.0 and dv[1, :, valid[1]:].abs().max().item() == 0.0
     assert dk[1, :, :valid[1]].abs().max().item() > 0.0
-    rows = torch.arange(0, Sq, 16, device=d)
-    for b, h in ((0, 3), (1, 30)):
-        kh, vh = k[b, h // 4, :valid[b]].float(), v[b, h // 4, :valid[b]].float()
-        s = (q[b, h, rows].float() @ kh.t()) * SCALE
-        ref = torch.softmax(s, -1) @ vh
-        assert (o[b, h, rows].float() - ref).abs().max().item() <= 2e-2
-        assert (L.view(Bz, HQ, Sq)[b, h, rows] - torch.logsumexp(s, -1)).abs().max().item() <= 1e-3
-        # dV rows of a few keys: dV[j] = sum_i P[i,j] dO[i]  over the 4 query heads of the group and all rows
-        hk = h // 4
-        keys = torch.tensor([0, 12345, valid[b] - 1], device=d)
-        acc = torch.zeros(3, 128, device=d)
-        for hq in range(hk * 4, hk * 4 + 4):
-            sc = (q[b, hq].float() @ k[b, hk, keys].float().t()) * SCALE           # [Sq, 3]
-            p = torch.exp(sc - L.view(Bz, HQ, Sq)[b, hq][:, None])
-            acc += p.t() @ do[b, hq].float()
-        assert (dv[b, hk, keys].float() - acc).abs().max().item() <= 2e-2
+    check_groups("config5", [(0, 0), (1, 7)], q, k, v, do, o, L, dq, dk, dv, valid)

@@ -29,7 +29,7 @@ extern "C" {
 
 #define LVX_ABI_VERSION 1
 
-enum lvx_dtype { LVX_BF16 = 0, LVX_FP16 = 1, LVX_FP32 = 2 /* computed with TF32 tensor-core operands */ };
+enum lvx_dtype { LVX_BF16 = 0, LVX_FP16 = 1, LVX_FP32 = 2 /* exact fp32 on the FP32-FMA pipe, no TF32 */ };
 
 enum lvx_error {
   LVX_OK = 0,
@@ -70,6 +70,12 @@ const char* lvx_last_error(void);
  * returns at once without computing. The reference has no equivalent: its waits are unbounded
  * (lv_xattn/async_communication.py:301-305). */
 int lvx_device_status(void* stream, int* status_out);
+
+/* Non-blocking look at the same word: enqueues, on `stream`, a copy of the word into *host_out (which should
+ * be pinned host memory that stays valid until the stream reaches the copy) and returns at once. The word is
+ * not cleared. Lets a host loop notice a bounded wait that ran out (a lost or very late peer) one call later
+ * without synchronising; the reference would simply block for ever (lv_xattn/async_communication.py:301-305). */
+int lvx_device_status_peek(void* stream, int* host_out);
 
 /* Bytes of scratch the forward / backward block kernels need for this shape.
  * Stands in for the per-step torch allocations in lv_xattn/attn.py:382-385 and
@@ -142,7 +148,8 @@ int lvx_add_cast(const float* a, const float* b, void* out, int out_dtype, size_
  * caller workspace. The number of K/V splits is lowered until the partials fit; a shape whose
  * unsplit partials exceed the area (more than about 64,500 rows B*Hq*Sq) is refused with
  * LVX_ERR_LIMIT. The first call on a device looks up the area's device address; make that first
- * call outside any stream capture. All calls share the area, which keeps the previous call's
+ * call outside any stream capture, and not from two host threads at once (the per-device address cache is
+ * filled without a lock). All calls share the area, which keeps the previous call's
  * contents (the kernel overwrites every entry it later reads, so nothing needs clearing); two calls
  * whose kernels overlap on the GPU -- different streams or devices' streams on one GPU -- race on it. */
 int lvx_fwd_block_static(const lvx_shape* s, const void* q, const void* k, const void* v,
@@ -151,7 +158,8 @@ int lvx_fwd_block_static(const lvx_shape* s, const void* q, const void* k, const
 
 /* ---- Exchange over peer-mapped memory (NVLink / NVSwitch) ------------------------------------------------
  * The reference moves blocks between ranks with torch.distributed batch_isend_irecv
- * (lv_xattn/async_communication.py:138-233) and reduces after each hop. These entry points do the same
+ * (send_recv_fwd_q, send_recv_fwd_Lo, send_recv_bwd_comp_reqs, send_recv_bwd_rescale_reqs and
+ * launch_async_handles, lv_xattn/async_communication.py:210-299) and reduces after each hop. These entry points do the same
  * exchanges with the library's own kernels reading the peers' memory directly; they need one buffer per
  * rank that every rank of the group has mapped (CUDA IPC / VMM; the Python host side uses torch's symmetric
  * memory). `lvx_peers.ptr[s]` is the address, in THIS process, of rank s's copy of that buffer; all copies
@@ -159,8 +167,8 @@ int lvx_fwd_block_static(const lvx_shape* s, const void* q, const void* k, const
  * such a buffer, zero at start: the producer calls lvx_p2p_signal(flags, slot, epoch) after the kernels that
  * fill its buffer (same stream), which stores `epoch` into word [slot][rank] of every peer's array; a pulling
  * call names its own array (`my_flags`, a device pointer), the slot and the epoch it needs and waits inside
- * the kernel, at most a few seconds, for all `world` words -- on time-out it reads nothing, and
- * lvx_device_status() returns 0x1300 | peer. Epochs of a slot must increase by one per use (compared
+ * the kernel, at most lvx_p2p_set_timeout() seconds (120 unless changed), for all `world` words -- on time-out
+ * it reads nothing, and lvx_device_status() returns 0x1300 | peer. Epochs of a slot must increase by one per use (compared
  * modulo 2^32); a buffer may be rewritten two epochs after it was signalled, so callers alternate two. */
 #define LVX_MAX_PEERS 16
 #define LVX_P2P_SLOTS 8
@@ -168,13 +176,19 @@ typedef struct lvx_peers {
   int32_t world;                      /* ranks in the group (<= LVX_MAX_PEERS) */
   int32_t rank;                       /* this rank */
   const void* ptr[LVX_MAX_PEERS];     /* ptr[s]: rank s's buffer as mapped in this process (16-byte aligned) */
+  size_t nbytes;                      /* size of every rank's buffer; offsets and extents are checked against it
+                                       * on the host before anything is launched (LVX_ERR_LIMIT) */
 } lvx_peers;
+
+/* Limit, in seconds, of the in-kernel wait for a peer's flag (all lvx_p2p_* calls of this process; 120 s at
+ * start). The reference's wait_async_handles blocks without limit (lv_xattn/async_communication.py:301-305). */
+int lvx_p2p_set_timeout(double seconds);
 
 /* Publishes `epoch` for `slot` to every rank (stream-ordered after the producer kernels). */
 int lvx_p2p_signal(const lvx_peers* flags, int slot, uint32_t epoch, void* stream);
 /* All-gather by pulling: dst + s*dst_stride <- rank s's bytes [src_offset, src_offset+bytes) for every s
- * (this rank included). Replaces send_recv_fwd_q / the backward slab exchange of the reference
- * (lv_xattn/async_communication.py:138-169) when every rank needs every block. */
+ * (this rank included). Replaces send_recv_fwd_q / send_recv_bwd_comp_reqs of the reference
+ * (lv_xattn/async_communication.py:210-227, :247-273) when every rank needs every block. */
 int lvx_p2p_gather(const lvx_peers* src, size_t src_offset, size_t bytes, void* dst, size_t dst_stride,
                    const uint32_t* my_flags, int slot, uint32_t epoch, void* stream);
 /* lvx_fwd_merge_parts with partial c read from rank c's buffer: O fp32 [B*Hq*Sq*D] at byte o_offset, lse
@@ -193,8 +207,8 @@ int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_d
  * all-to-all) to dst->ptr[s] + dst_offset + rank*dst_rank_stride. The consumer calls lvx_p2p_wait (a one-block
  * kernel with the bounded wait described above) and then runs the ordinary kernels on its own buffer:
  * lvx_fwd_block / lvx_bwd_block on gathered blocks, lvx_fwd_merge_parts / lvx_sum_cast on received partials.
- * Replaces send_recv_fwd_q, send_recv_fwd_Lo, send_recv_bwd_comp, send_recv_bwd_dq + wait_async_handles
- * (lv_xattn/async_communication.py:138-233, :301-305). */
+ * Replaces send_recv_fwd_q, send_recv_fwd_Lo, send_recv_bwd_comp_reqs, send_recv_bwd_rescale_reqs +
+ * wait_async_handles (lv_xattn/async_communication.py:210-289, :301-305). */
 #define LVX_P2P_MAX_SEGMENTS 4
 typedef struct lvx_push_segment {
   const void* src;
@@ -202,6 +216,8 @@ typedef struct lvx_push_segment {
   size_t dst_offset;
   size_t dst_rank_stride;
   size_t bytes;
+  size_t src_bytes;   /* size of the source allocation (0 = not checked): an all-to-all segment reads
+                       * world*src_stride bytes from it */
 } lvx_push_segment;
 int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
                  uint32_t epoch, void* stream);

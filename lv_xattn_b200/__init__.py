@@ -28,3 +28,4 @@ from .hf_patch import (  # noqa: F401,E402
     set_global_cross_attention_states,
 )
 from .host_io import HostStreamedAttention  # noqa: F401,E402
+from .peer_memory import check_device_status  # noqa: F401,E402

@@ -18,7 +18,8 @@ _DTYPE = {torch.bfloat16: LVX_BF16, torch.float16: LVX_FP16, torch.float32: LVX_
 
 # every symbol include/lvx.h declares
 SYMBOLS = [
-    "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_query_workspace", "lvx_fwd_block",
+    "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_device_status_peek", "lvx_p2p_set_timeout",
+    "lvx_query_workspace", "lvx_fwd_block",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
     "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
     "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast", "lvx_p2p_push", "lvx_p2p_wait",
@@ -32,12 +33,13 @@ class LvxShape(ctypes.Structure):
 
 
 class LvxPeers(ctypes.Structure):
-    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("ptr", ctypes.c_void_p * 16)]
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("ptr", ctypes.c_void_p * 16),
+                ("nbytes", ctypes.c_size_t)]
 
 
 class LvxPushSegment(ctypes.Structure):
     _fields_ = [("src", ctypes.c_void_p), ("src_stride", ctypes.c_size_t), ("dst_offset", ctypes.c_size_t),
-                ("dst_rank_stride", ctypes.c_size_t), ("bytes", ctypes.c_size_t)]
+                ("dst_rank_stride", ctypes.c_size_t), ("bytes", ctypes.c_size_t), ("src_bytes", ctypes.c_size_t)]
 
 
 class LvxError(RuntimeError):
@@ -62,6 +64,8 @@ def load():
     lib.lvx_version.restype = ctypes.c_int
     lib.lvx_last_error.restype = ctypes.c_char_p
     lib.lvx_device_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int)]
+    lib.lvx_device_status_peek.argtypes = [vp, vp]
+    lib.lvx_p2p_set_timeout.argtypes = [ctypes.c_double]
     lib.lvx_query_workspace.argtypes = [sp, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
     lib.lvx_fwd_block.argtypes = [sp, vp, vp, vp, i32p, ctypes.c_float, vp, ctypes.c_size_t, vp]
     lib.lvx_fwd_combine_merge.argtypes = [sp, vp, fp, fp, vp, fp, ctypes.c_int, vp]

@@ -235,7 +235,7 @@ def wait_async_handles(reqs, timeout_s: float | None = None):
             try:
                 ok = r.wait(datetime.timedelta(seconds=limit))
             except RuntimeError as e:
-                if "imeout" in str(e) or "timed out" in str(e):
+                if "timeout" in str(e).lower() or "timed out" in str(e).lower():
                     raise P2PTimeoutError(f"P2P wait exceeded {limit} s: {e}") from e
                 raise
             if ok is False:

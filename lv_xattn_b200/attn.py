@@ -144,6 +144,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         sched = "gather"          # picked by "auto": the exchange kernels copy 16 bytes at a time
     if sched == "p2p":
         from . import peer_memory as pm
+        pm.status_watch.poll()
         flag_peers, my_flags = pm.get_flags(dev)
         # every rank stores its Q block into all ranks' gathered buffer (posted NVLink stores) and signals
         e = pm.next_epoch(pm.SLOT_FWD_Q)
@@ -168,9 +169,11 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         o_recv = _carve(pbuf.local, p_off, (W, B, Hq, Sq, D), torch.float32)
         l_recv = _carve(pbuf.local, p_off + W * n_o * 4, (W, B * Hq, Sq), torch.float32)
         ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
+        pm.status_watch.post()
         return q, k, v, o, L
     if sched == "p2p_pull":
         from . import peer_memory as pm
+        pm.status_watch.poll()
         rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
         # the Q block is published in a peer-mapped buffer and every rank pulls all W of them
@@ -193,6 +196,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         ops.p2p_signal(flag_peers, pm.SLOT_FWD_PARTS, e)
         ops.p2p_fwd_merge(pbuf.peers, p_off + rank * n_o * 4, p_off + W * n_o * 4 + rank * n_l * 4, o, L, my_flags,
                           pm.SLOT_FWD_PARTS, e)
+        pm.status_watch.post()
         return q, k, v, o, L
     if sched == "gather":
         q_all = _carve(get_slabs("g_q", W * n_o * es, dev, 1)[0], 0, (W, B, Hq, Sq, D), dt)
@@ -253,6 +257,15 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
     return q, k, v, o, L
 
 
+def _end_of_backward_status(pm):
+    """Peer-memory schedules: a flag wait that ran out leaves the outputs unwritten. The status word is copied to
+    the host after the last kernel and read at the start of the next call (no host synchronisation); with
+    LVX_STATUS_CHECK=sync it is read here, at the price of one synchronisation per backward."""
+    pm.status_watch.post()
+    if os.environ.get("LVX_STATUS_CHECK", "") == "sync":
+        pm.status_watch.check()
+
+
 def _exchange_final(o_send, l_send, o_recv, l_recv, comm_mode):
     return _exchange([o_send, l_send], [o_recv, l_recv], comm_mode)
 
@@ -275,9 +288,6 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
 
     n_q, n_r, n_kv = B * Hq * Sq * D, B * Hq * Sq, B * Hkv * Skv * D
     delta = ops.bwd_prep(oc, doc)                       # once, at home; travels instead of O
-    acc = get_slabs("bwd_dkdv", 2 * n_kv * 4, dev, 1)[0]
-    dk_acc = _carve(acc, 0, (B, Hkv, Skv, D), torch.float32)
-    dv_acc = _carve(acc, n_kv * 4, (B, Hkv, Skv, D), torch.float32)
     dq = torch.empty(B, Hq, Sq, D, dtype=dt, device=dev)
 
     sched = _schedule(schedule, q) if W > 1 else "gather"
@@ -296,6 +306,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         sched = "gather"          # picked by "auto": the exchange kernels copy 16 bytes at a time
     if sched == "p2p":
         from . import peer_memory as pm
+        pm.status_watch.poll()
         flag_peers, my_flags = pm.get_flags(dev)
         e = pm.next_epoch(pm.SLOT_BWD_IN)
         blk = W * (2 * n_q * es + 2 * n_r * 4)
@@ -321,9 +332,11 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         ops.p2p_push(dbuf.peers, flag_peers, [(dq_parts, True, d_off, n_q * 4)], pm.SLOT_BWD_DQ, e)
         ops.p2p_wait(my_flags, W, pm.SLOT_BWD_DQ, e)
         ops.sum_cast(_carve(dbuf.local, d_off, (W, B, Hq, Sq, D), torch.float32), dt, out=dq)
+        _end_of_backward_status(pm)
         return dq, dk, dv
     elif sched == "p2p_pull":
         from . import peer_memory as pm
+        pm.status_watch.poll()
         rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
         e = pm.next_epoch(pm.SLOT_BWD_IN)
@@ -354,6 +367,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         ops.bwd_block(q_all, do_all, l_all, d_all, kc, vc, sm_scale, dq_parts, dk, dv, "final", kvl)
         ops.p2p_signal(flag_peers, pm.SLOT_BWD_DQ, e)
         ops.p2p_sum_cast(dbuf.peers, d_off + rank * n_q * 4, dq, my_flags, pm.SLOT_BWD_DQ, e)   # each owner sums its block
+        _end_of_backward_status(pm)
         return dq, dk, dv
     elif sched == "gather":
         gbuf = get_slabs("g_bwd_in", W * (2 * n_q * es + 2 * n_r * 4), dev, 1)[0]
@@ -375,6 +389,10 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
     else:
         slab_bytes = 2 * n_q * es + 2 * n_r * 4
         in_bufs, send_bufs, recv_bufs = maybe_get_set_global_memory_buffer_bwd(slab_bytes, n_q * 4, dev)
+        # fp32 dK/dV accumulate across the W steps (only this schedule revisits the shard)
+        acc = get_slabs("bwd_dkdv", 2 * n_kv * 4, dev, 1)[0]
+        dk_acc = _carve(acc, 0, (B, Hkv, Skv, D), torch.float32)
+        dv_acc = _carve(acc, n_kv * 4, (B, Hkv, Skv, D), torch.float32)
         dq_delta = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
 
         def slab_views(buf):

@@ -142,6 +142,15 @@ int lvx_device_status(void* stream, int* status_out) {
   return LVX_OK;
 }
 
+int lvx_device_status_peek(void* stream, int* host_out) {
+  if (!host_out) return fail(LVX_ERR_NULL, "lvx_device_status_peek: host_out is NULL");
+  int* sp = status_ptr();
+  if (!sp) return fail(LVX_ERR_DRIVER, "lvx_device_status_peek: status word unavailable");
+  cudaError_t e = cudaMemcpyAsync(host_out, sp, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyAsync(status peek)");
+  return LVX_OK;
+}
+
 int lvx_query_workspace(const lvx_shape* s, size_t* fwd_bytes, size_t* bwd_bytes) {
   int rc = check_shape(s, "lvx_query_workspace");
   if (rc) return rc;

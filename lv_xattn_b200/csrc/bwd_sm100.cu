@@ -97,18 +97,21 @@ struct BwdParams {
   float* dk_acc;       // [slab][skv][128]  (fp32; 16-bit when accumulate == 2)
   float* dv_acc;
   int accumulate;      // 0 overwrite fp32, 1 add to fp32, 2 write the finished gradient in the input dtype
-  int debug;           // development switches (LVX_BWD_DEBUG); 0 in normal use
   int* status;
 };
 
-// Development aid, compiled into a separate instantiation that runs only when LVX_BWD_DEBUG is set (bit 128:
-// cycle stamps of CTA (0,0), tiles 4..11, 16 slots per tile and role; bit 1: the dQ reduce-adds are skipped).
+// Development aid, compiled only with -DLVX_DEV_STAMPS (never in the shipped library): cycle stamps of CTA
+// (0,0), tiles 4..11, 16 slots per tile and role, printed by the launcher.
+#ifdef LVX_DEV_STAMPS
 __device__ long long g_bwd_ts[2 * 8 * 16];
 #define BWD_TS(role, slot)                                                                         \
   do {                                                                                             \
-    if (DBG && (p.debug & 128) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && j >= 4 && j < 12)    \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && j >= 4 && j < 12)                       \
       g_bwd_ts[((role) * 8 + (j - 4)) * 16 + (slot)] = clock64();                                  \
   } while (0)
+#else
+#define BWD_TS(role, slot) do {} while (0)
+#endif
 
 #define BWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x200 | ((role) << 5) | (bar))
 
@@ -118,7 +121,7 @@ __device__ __forceinline__ float2 unpack16x2(uint32_t v) {
   return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
-template <bool IS_BF16, bool DBG>
+template <bool IS_BF16>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
            const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, const BwdParams p) {
@@ -363,7 +366,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);     // Y is free for the next tile's dP^T
         if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 6);
-        if (!DBG || !(p.debug & 1)) {
+        {
           const int row0 = (j % nq) * 128 + ch * 64;
           const int ncols = min(64, p.rows - row0);
           float* dst = p.dq_acc + (size_t(slab + (j / nq) * p.kv_slabs) * p.rows + row0) * 128 + d;
@@ -539,6 +542,8 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
                      const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                      float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st) {
   if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "lvx_bwd_block: sm_scale must be positive");
+  if (accumulate_dkdv < 0 || accumulate_dkdv > 2)
+    return fail(LVX_ERR_SHAPE, "lvx_bwd_block: accumulate_dkdv must be 0, 1 or 2 (got %d)", accumulate_dkdv);
   if (s.dtype == LVX_FP32)
     return launch_bwd_block_fp32(s, q, d_o, lse, delta, k, v, kv_valid_len, sm_scale, dq_acc, dk_acc, dv_acc,
                                  accumulate_dkdv, st);
@@ -571,10 +576,6 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   p.dv_acc = dv_acc;
   p.accumulate = accumulate_dkdv;
   p.status = status;
-  {
-    const char* dbg = getenv("LVX_BWD_DEBUG");
-    p.debug = dbg ? atoi(dbg) : 0;
-  }
 
   dim3 grid((s.Skv + 127) / 128, s.B * s.Hkv, 1);
   cudaError_t e = cudaSuccess;
@@ -582,17 +583,13 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
     if (e == cudaSuccess) kern<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tmQ, tmDO, tmK, tmV, p);
   };
-  if (s.dtype == LVX_BF16) {
-    if (p.debug) go(bwd_kernel<true, true>);
-    else go(bwd_kernel<true, false>);
-  } else {
-    if (p.debug) go(bwd_kernel<false, true>);
-    else go(bwd_kernel<false, false>);
-  }
+  if (s.dtype == LVX_BF16) go(bwd_kernel<true>);
+  else go(bwd_kernel<false>);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(bwd)");
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "bwd_kernel launch");
-  if (p.debug & 128) {
+#ifdef LVX_DEV_STAMPS
+  {
     static long long ts[2 * 8 * 16];
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(ts, g_bwd_ts, sizeof(ts));
@@ -605,6 +602,7 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
         fprintf(stderr, "\n");
       }
   }
+#endif
   return LVX_OK;
 }
 

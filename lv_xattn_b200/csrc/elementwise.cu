@@ -14,6 +14,12 @@ namespace lvx {
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// While the device status word is set (a bounded wait ran out somewhere) every kernel returns at once, so that
+// nothing is computed from buffers an aborted kernel left unwritten.
+__device__ __forceinline__ bool poisoned(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+
 template <int OUT>  // 0 bf16, 1 fp16, 2 fp32
 __device__ __forceinline__ void store4(void* base, size_t idx4, float4 v) {
   if (OUT == 2) {
@@ -54,7 +60,8 @@ template <int OUT>
 __global__ void __launch_bounds__(256)
 fwd_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part, const float* __restrict__ o_in,
                    const float* __restrict__ lse_in, void* __restrict__ o_out, float* __restrict__ lse_out,
-                   int rows_per_slab, int nsplit, long total_rows) {
+                   int rows_per_slab, int nsplit, long total_rows, const int* status) {
+  if (poisoned(status)) return;
   const int lane = threadIdx.x & 31;
   const long grow = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (grow >= total_rows) return;
@@ -121,14 +128,15 @@ int launch_fwd_combine(const lvx_shape& s, const FwdPlan& p, const float* o_part
                        cudaStream_t st) {
   const long total_rows = long(q_blocks_of(s)) * s.B * s.Hq * s.Sq;
   const int threads = 256;
+  const int* sp = device_status_ptr();
   const long blocks = (total_rows * 32 + threads - 1) / threads;
   const int out = out_is_final ? s.dtype : LVX_FP32;
   if (out == LVX_BF16)
-    fwd_combine_kernel<0><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows);
+    fwd_combine_kernel<0><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows, sp);
   else if (out == LVX_FP16)
-    fwd_combine_kernel<1><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows);
+    fwd_combine_kernel<1><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows, sp);
   else
-    fwd_combine_kernel<2><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows);
+    fwd_combine_kernel<2><<<blocks, threads, 0, st>>>(o_part, ml_part, o_in, lse_in, o_out, lse_out, p.rows, p.nsplit, total_rows, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_combine launch");
   return LVX_OK;
@@ -140,7 +148,8 @@ template <int OUT>
 __global__ void __launch_bounds__(256)
 fwd_merge_parts_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int count,
                        size_t stride_o, size_t stride_lse, void* __restrict__ o_out, float* __restrict__ lse_out,
-                       long total_rows) {
+                       long total_rows, const int* status) {
+  if (poisoned(status)) return;
   const int lane = threadIdx.x & 31;
   const long row = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= total_rows) return;
@@ -168,13 +177,14 @@ int launch_fwd_merge_parts(const lvx_shape& s, const float* o_parts, const float
                            size_t stride_o, size_t stride_lse, void* o_out, float* lse_out, cudaStream_t st) {
   const long total_rows = long(q_blocks_of(s)) * s.B * s.Hq * s.Sq;
   const int threads = 256;
+  const int* sp = device_status_ptr();
   const long blocks = (total_rows * 32 + threads - 1) / threads;
   if (s.dtype == LVX_BF16)
-    fwd_merge_parts_kernel<0><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows);
+    fwd_merge_parts_kernel<0><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows, sp);
   else if (s.dtype == LVX_FP16)
-    fwd_merge_parts_kernel<1><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows);
+    fwd_merge_parts_kernel<1><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows, sp);
   else
-    fwd_merge_parts_kernel<2><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows);
+    fwd_merge_parts_kernel<2><<<blocks, threads, 0, st>>>(o_parts, lse_parts, count, stride_o, stride_lse, o_out, lse_out, total_rows, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_merge_parts launch");
   return LVX_OK;
@@ -183,7 +193,9 @@ int launch_fwd_merge_parts(const lvx_shape& s, const float* o_parts, const float
 // ---------------------------------------------------------------------------------------------
 template <int IN>
 __global__ void __launch_bounds__(256)
-bwd_prep_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta, long total_rows) {
+bwd_prep_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float* __restrict__ delta, long total_rows,
+                const int* status) {
+  if (poisoned(status)) return;
   const int lane = threadIdx.x & 31;
   const long row = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= total_rows) return;
@@ -198,10 +210,11 @@ bwd_prep_kernel(const void* __restrict__ o, const void* __restrict__ d_o, float*
 int launch_bwd_prep(const lvx_shape& s, const void* o, const void* d_o, float* delta, cudaStream_t st) {
   const long total_rows = long(q_blocks_of(s)) * s.B * s.Hq * s.Sq;
   const int threads = 256;
+  const int* sp = device_status_ptr();
   const long blocks = (total_rows * 32 + threads - 1) / threads;
-  if (s.dtype == LVX_BF16) bwd_prep_kernel<0><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows);
-  else if (s.dtype == LVX_FP16) bwd_prep_kernel<1><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows);
-  else bwd_prep_kernel<2><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows);
+  if (s.dtype == LVX_BF16) bwd_prep_kernel<0><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows, sp);
+  else if (s.dtype == LVX_FP16) bwd_prep_kernel<1><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows, sp);
+  else bwd_prep_kernel<2><<<blocks, threads, 0, st>>>(o, d_o, delta, total_rows, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "bwd_prep launch");
   return LVX_OK;
@@ -210,7 +223,9 @@ int launch_bwd_prep(const lvx_shape& s, const void* o, const void* d_o, float* d
 // ---------------------------------------------------------------------------------------------
 template <int OUT>
 __global__ void __launch_bounds__(256)
-add_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, void* __restrict__ out, size_t n4, size_t n) {
+add_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, void* __restrict__ out, size_t n4, size_t n,
+                const int* status) {
+  if (poisoned(status)) return;
   const size_t stride = size_t(gridDim.x) * blockDim.x;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
     float4 v = reinterpret_cast<const float4*>(a)[i];
@@ -233,12 +248,13 @@ add_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, void* 
 int launch_add_cast(const float* a, const float* b, void* out, int out_dtype, size_t n, cudaStream_t st) {
   const size_t n4 = n / 4;
   const int threads = 256;
+  const int* sp = device_status_ptr();
   size_t blocks = (n4 + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks == 0) blocks = 1;
-  if (out_dtype == LVX_BF16) add_cast_kernel<0><<<blocks, threads, 0, st>>>(a, b, out, n4, n);
-  else if (out_dtype == LVX_FP16) add_cast_kernel<1><<<blocks, threads, 0, st>>>(a, b, out, n4, n);
-  else add_cast_kernel<2><<<blocks, threads, 0, st>>>(a, b, out, n4, n);
+  if (out_dtype == LVX_BF16) add_cast_kernel<0><<<blocks, threads, 0, st>>>(a, b, out, n4, n, sp);
+  else if (out_dtype == LVX_FP16) add_cast_kernel<1><<<blocks, threads, 0, st>>>(a, b, out, n4, n, sp);
+  else add_cast_kernel<2><<<blocks, threads, 0, st>>>(a, b, out, n4, n, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "add_cast launch");
   return LVX_OK;
@@ -247,7 +263,9 @@ int launch_add_cast(const float* a, const float* b, void* out, int out_dtype, si
 // ---------------------------------------------------------------------------------------------
 template <int OUT>
 __global__ void __launch_bounds__(256)
-sum_cast_kernel(const float* __restrict__ parts, int count, size_t stride, void* __restrict__ out, size_t n4) {
+sum_cast_kernel(const float* __restrict__ parts, int count, size_t stride, void* __restrict__ out, size_t n4,
+                const int* status) {
+  if (poisoned(status)) return;
   const size_t gstride = size_t(gridDim.x) * blockDim.x;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += gstride) {
     float4 v = reinterpret_cast<const float4*>(parts)[i];
@@ -262,12 +280,13 @@ sum_cast_kernel(const float* __restrict__ parts, int count, size_t stride, void*
 int launch_sum_cast(const float* parts, int count, size_t stride, void* out, int out_dtype, size_t n, cudaStream_t st) {
   const size_t n4 = n / 4;
   const int threads = 256;
+  const int* sp = device_status_ptr();
   size_t blocks = (n4 + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks == 0) blocks = 1;
-  if (out_dtype == LVX_BF16) sum_cast_kernel<0><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4);
-  else if (out_dtype == LVX_FP16) sum_cast_kernel<1><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4);
-  else sum_cast_kernel<2><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4);
+  if (out_dtype == LVX_BF16) sum_cast_kernel<0><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4, sp);
+  else if (out_dtype == LVX_FP16) sum_cast_kernel<1><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4, sp);
+  else sum_cast_kernel<2><<<blocks, threads, 0, st>>>(parts, count, stride, out, n4, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "sum_cast launch");
   return LVX_OK;

@@ -36,10 +36,12 @@ struct Fp32FwdParams {
   int rows, skv, hkv, kv_slabs, nsplit, tiles_per_split;   // tiles_per_split counts 128-row tiles, as in the 16-bit plan
   float scale_log2;
   float *o_part, *ml_part;
+  const int* status;   // device status word: non-zero => return at once
 };
 
 __global__ void __launch_bounds__(256)
 fp32_fwd_kernel(const Fp32FwdParams p) {
+  if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
   extern __shared__ float sm[];
   float* sQ = sm;
   float* sK = sQ + SM_TILE;
@@ -149,10 +151,12 @@ struct Fp32BwdParams {
   float scale, scale_log2;
   float *dq_acc, *dk_acc, *dv_acc;
   int accumulate;
+  const int* status;   // device status word: non-zero => return at once
 };
 
 __global__ void __launch_bounds__(256)
 fp32_bwd_kernel(const Fp32BwdParams p) {
+  if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
   extern __shared__ float sm[];
   float* sK = sm;
   float* sV = sK + SM_TILE;
@@ -310,6 +314,7 @@ int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, 
   p.scale_log2 = sm_scale * 1.4426950408889634f;
   p.o_part = o_part;
   p.ml_part = ml_part;
+  p.status = device_status_ptr();
   const int smem = (3 * SM_TILE + SM_PTILE) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(fp32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 fwd)");
@@ -342,6 +347,7 @@ int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, co
   p.dk_acc = dk_acc;
   p.dv_acc = dv_acc;
   p.accumulate = accumulate_dkdv;
+  p.status = device_status_ptr();
   const int smem = (4 * SM_TILE + 2 * SM_PTILE) * sizeof(float);
   cudaError_t e = cudaFuncSetAttribute(fp32_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 bwd)");

@@ -58,22 +58,25 @@ struct FwdParams {
   float scale_log2;     // sm_scale * log2(e)
   float* o_part;        // [B*Hkv][nsplit][rows][128]
   float* ml_part;       // [B*Hkv][nsplit][rows][2]
-  int debug;
   int* status;
 };
 
-// Development aid (LVX_FWD_DEBUG=1): cycle stamps of CTA (0,0,0), K/V tiles 4..11, 8 slots per tile and role.
-// The stamped kernel is a separate instantiation: even the untaken test costs the lone softmax warps ~2 %.
+// Development aid, compiled only with -DLVX_DEV_STAMPS (never in the shipped library): cycle stamps of CTA
+// (0,0,0), K/V tiles 4..11, 8 slots per tile and role, printed by the launcher.
+#ifdef LVX_DEV_STAMPS
 __device__ long long g_fwd_ts[3 * 8 * 8];
 #define FWD_TS(role, slot)                                                                              \
   do {                                                                                                  \
-    if (STAMPS && p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && j >= 4 && j < 12) \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && j >= 4 && j < 12)         \
       g_fwd_ts[((role) * 8 + (j - 4)) * 8 + (slot)] = clock64();                                        \
   } while (0)
+#else
+#define FWD_TS(role, slot) do {} while (0)
+#endif
 
 #define FWD_CODE(role, bar) (LVX_DEV_TIMEOUT_BASE | 0x100 | ((role) << 5) | (bar))
 
-template <bool IS_BF16, bool STAMPS>
+template <bool IS_BF16>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
@@ -521,7 +524,6 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   p.o_part = o_part;
   p.ml_part = ml_part;
   p.status = status;
-  p.debug = getenv("LVX_FWD_DEBUG") ? 1 : 0;
 
   dim3 grid(pl.m_blocks, qb * s.B * s.Hkv, pl.nsplit);
   cudaError_t e = cudaSuccess;
@@ -529,17 +531,13 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
     if (e == cudaSuccess) kern<<<grid, FWD_THREADS, FWD_SMEM, st>>>(tmQ, tmK, tmV, p);
   };
-  if (s.dtype == LVX_BF16) {
-    if (p.debug) go(fwd_kernel<true, true>);
-    else go(fwd_kernel<true, false>);
-  } else {
-    if (p.debug) go(fwd_kernel<false, true>);
-    else go(fwd_kernel<false, false>);
-  }
+  if (s.dtype == LVX_BF16) go(fwd_kernel<true>);
+  else go(fwd_kernel<false>);
   if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fwd)");
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "fwd_kernel launch");
-  if (p.debug) {
+#ifdef LVX_DEV_STAMPS
+  {
     static long long ts[3 * 8 * 8];
     cudaDeviceSynchronize();
     cudaMemcpyFromSymbol(ts, g_fwd_ts, sizeof(ts));
@@ -551,6 +549,7 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
         fprintf(stderr, "\n");
       }
   }
+#endif
   return LVX_OK;
 }
 

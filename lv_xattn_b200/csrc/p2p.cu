@@ -27,9 +27,22 @@
 
 namespace lvx {
 
-// A peer may legitimately be late by more than a kernel's worth of time (host-side jitter between ranks), so
-// the wait for its flag is given eight times the limit of the in-kernel pipeline waits: about eight seconds.
-constexpr long long P2P_WAIT_LIMIT_CYCLES = 8 * LVX_SPIN_LIMIT_CYCLES;
+// A peer may legitimately be late by far more than a kernel's worth of time (a checkpoint write, a data-loader
+// stall, an evaluation on one rank), so the wait for its flag has its own limit, set at run time in seconds
+// (lvx_p2p_set_timeout; 120 s unless changed) and converted to SM cycles with the device's peak clock.
+static double g_wait_seconds = 120.0;
+static long long wait_limit_cycles() {
+  static int khz[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 120ll * 2000000000ll;
+  if (!khz[dev]) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, dev) != cudaSuccess || v <= 0) v = 2000000;
+    khz[dev] = v;
+  }
+  const double cycles = g_wait_seconds * 1e3 * double(khz[dev]);
+  return cycles < 1e3 ? 1000ll : (cycles > 9e18 ? (long long)9e18 : (long long)cycles);
+}
 
 struct PeerPtrs {
   const uint8_t* p[LVX_MAX_PEERS];
@@ -51,7 +64,8 @@ __device__ __forceinline__ float4 ld_cg_f4(const void* p) {
 }
 
 // Every block waits for all peers (thread 0 polls, the rest wait at the barrier). Returns false on time-out.
-__device__ __forceinline__ bool p2p_wait_all(const uint32_t* my_flags, int world, int slot, uint32_t epoch, int* status) {
+__device__ __forceinline__ bool p2p_wait_all(const uint32_t* my_flags, int world, int slot, uint32_t epoch, int* status,
+                                             long long limit_cycles) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) {
     int ok = (*reinterpret_cast<volatile int*>(status) == 0) ? 1 : 0;
@@ -59,7 +73,7 @@ __device__ __forceinline__ bool p2p_wait_all(const uint32_t* my_flags, int world
     for (int s = 0; s < world && ok; ++s) {
       const uint32_t* f = my_flags + slot * LVX_MAX_PEERS + s;
       while (static_cast<int32_t>(ld_acquire_sys(f) - epoch) < 0) {
-        if (clock64() - t0 > P2P_WAIT_LIMIT_CYCLES) {
+        if (clock64() - t0 > limit_cycles) {
           atomicCAS(status, 0, LVX_DEV_TIMEOUT_BASE | 0x300 | s);
           ok = 0;
           break;
@@ -84,8 +98,8 @@ __global__ void p2p_signal_kernel(PeerPtrs flags, int world, int rank, int slot,
 // dst + s*dst_stride <- peer s's [src_offset, src_offset + bytes) for every s; bytes is a multiple of 16.
 __global__ void __launch_bounds__(256)
 p2p_gather_kernel(PeerPtrs src, size_t src_offset, size_t bytes, uint8_t* __restrict__ dst, size_t dst_stride, int world,
-                  const uint32_t* my_flags, int slot, uint32_t epoch, int* status) {
-  if (!p2p_wait_all(my_flags, world, slot, epoch, status)) return;
+                  const uint32_t* my_flags, int slot, uint32_t epoch, int* status, long long limit) {
+  if (!p2p_wait_all(my_flags, world, slot, epoch, status, limit)) return;
   const size_t n16 = bytes >> 4;
   const size_t total = n16 * world;
   const size_t gstride = size_t(gridDim.x) * blockDim.x;
@@ -115,8 +129,8 @@ template <int OUT>
 __global__ void __launch_bounds__(256)
 p2p_fwd_merge_kernel(PeerPtrs parts, size_t o_offset, size_t lse_offset, int world, void* __restrict__ o_out,
                      float* __restrict__ lse_out, long total_rows, const uint32_t* my_flags, int slot, uint32_t epoch,
-                     int* status) {
-  if (!p2p_wait_all(my_flags, world, slot, epoch, status)) return;
+                     int* status, long long limit) {
+  if (!p2p_wait_all(my_flags, world, slot, epoch, status, limit)) return;
   const int lane = threadIdx.x & 31;
   const long row = (long(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   if (row >= total_rows) return;
@@ -155,8 +169,8 @@ p2p_fwd_merge_kernel(PeerPtrs parts, size_t o_offset, size_t lse_offset, int wor
 template <int OUT>
 __global__ void __launch_bounds__(256)
 p2p_sum_cast_kernel(PeerPtrs parts, size_t offset, int world, void* __restrict__ out, size_t n4, const uint32_t* my_flags,
-                    int slot, uint32_t epoch, int* status) {
-  if (!p2p_wait_all(my_flags, world, slot, epoch, status)) return;
+                    int slot, uint32_t epoch, int* status, long long limit) {
+  if (!p2p_wait_all(my_flags, world, slot, epoch, status, limit)) return;
   const size_t gstride = size_t(gridDim.x) * blockDim.x;
   for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += gstride) {
     float4 v[LVX_MAX_PEERS];
@@ -220,8 +234,9 @@ p2p_push_kernel(PeerPtrs dst, PeerPtrs flags, PushArgs a, int world, int rank, i
   }
 }
 
-__global__ void p2p_wait_kernel(const uint32_t* my_flags, int world, int slot, uint32_t epoch, int* status) {
-  p2p_wait_all(my_flags, world, slot, epoch, status);
+__global__ void p2p_wait_kernel(const uint32_t* my_flags, int world, int slot, uint32_t epoch, int* status,
+                                long long limit) {
+  p2p_wait_all(my_flags, world, slot, epoch, status, limit);
 }
 
 static int peers_ok(const lvx_peers* p, const char* who) {
@@ -232,6 +247,15 @@ static int peers_ok(const lvx_peers* p, const char* who) {
     if (!p->ptr[i]) return fail(LVX_ERR_NULL, "%s: peer %d has no address", who, i);
     if (reinterpret_cast<uintptr_t>(p->ptr[i]) & 15u) return fail(LVX_ERR_ALIGN, "%s: peer %d address is not 16-byte aligned", who, i);
   }
+  return LVX_OK;
+}
+// [offset, offset + bytes) must lie inside every peer's mapping (host-side bounds check: a wrong offset would
+// otherwise become a load or store into another GPU's memory).
+static int range_ok(const lvx_peers* p, size_t offset, size_t bytes, const char* who, const char* what) {
+  if (p->nbytes == 0) return fail(LVX_ERR_SHAPE, "%s: the peer table carries no buffer size (nbytes = 0)", who);
+  if (offset > p->nbytes || bytes > p->nbytes - offset)
+    return fail(LVX_ERR_LIMIT, "%s: %s [%zu, +%zu) runs past the %zu-byte peer buffer", who, what, offset, bytes,
+                size_t(p->nbytes));
   return LVX_OK;
 }
 static PeerPtrs to_dev(const lvx_peers* p) {
@@ -256,6 +280,7 @@ int lvx_p2p_signal(const lvx_peers* flags, int slot, uint32_t epoch, void* strea
   int rc = peers_ok(flags, who);
   if (rc) return rc;
   if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  if ((rc = range_ok(flags, 0, sizeof(uint32_t) * LVX_P2P_SLOTS * LVX_MAX_PEERS, who, "the flag array"))) return rc;
   p2p_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_dev(flags), flags->world, flags->rank, slot, epoch);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
@@ -270,11 +295,13 @@ int lvx_p2p_gather(const lvx_peers* src, size_t src_offset, size_t bytes, void* 
   if ((bytes & 15u) || (src_offset & 15u) || (dst_stride & 15u) || (reinterpret_cast<uintptr_t>(dst) & 15u))
     return fail(LVX_ERR_ALIGN, "%s: sizes, offsets and dst must be multiples of 16 bytes", who);
   if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  if ((rc = range_ok(src, src_offset, bytes, who, "the source range"))) return rc;
   int* status = device_status_ptr();
   if (!status) return fail(LVX_ERR_DRIVER, "%s: no device status word", who);
   if (bytes == 0) return LVX_OK;
   p2p_gather_kernel<<<grid_for((bytes >> 4) * src->world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      to_dev(src), src_offset, bytes, static_cast<uint8_t*>(dst), dst_stride, src->world, my_flags, slot, epoch, status);
+      to_dev(src), src_offset, bytes, static_cast<uint8_t*>(dst), dst_stride, src->world, my_flags, slot, epoch, status,
+      wait_limit_cycles());
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
 }
@@ -291,16 +318,19 @@ int lvx_p2p_fwd_merge(const lvx_shape* s, const lvx_peers* parts, size_t o_offse
   int* status = device_status_ptr();
   if (!status) return fail(LVX_ERR_DRIVER, "%s: no device status word", who);
   const long total_rows = long(s->B) * s->Hq * s->Sq;
+  if ((rc = range_ok(parts, o_offset, size_t(total_rows) * 128 * sizeof(float), who, "the O partial"))) return rc;
+  if ((rc = range_ok(parts, lse_offset, size_t(total_rows) * sizeof(float), who, "the lse partial"))) return rc;
   const long blocks = (total_rows * 32 + 255) / 256;
   if (blocks == 0) return LVX_OK;
   const PeerPtrs d = to_dev(parts);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long lim = wait_limit_cycles();
   if (s->dtype == LVX_BF16)
-    p2p_fwd_merge_kernel<0><<<blocks, 256, 0, st>>>(d, o_offset, lse_offset, parts->world, o_out, lse_out, total_rows, my_flags, slot, epoch, status);
+    p2p_fwd_merge_kernel<0><<<blocks, 256, 0, st>>>(d, o_offset, lse_offset, parts->world, o_out, lse_out, total_rows, my_flags, slot, epoch, status, lim);
   else if (s->dtype == LVX_FP16)
-    p2p_fwd_merge_kernel<1><<<blocks, 256, 0, st>>>(d, o_offset, lse_offset, parts->world, o_out, lse_out, total_rows, my_flags, slot, epoch, status);
+    p2p_fwd_merge_kernel<1><<<blocks, 256, 0, st>>>(d, o_offset, lse_offset, parts->world, o_out, lse_out, total_rows, my_flags, slot, epoch, status, lim);
   else
-    p2p_fwd_merge_kernel<2><<<blocks, 256, 0, st>>>(d, o_offset, lse_offset, parts->world, o_out, lse_out, total_rows, my_flags, slot, epoch, status);
+    p2p_fwd_merge_kernel<2><<<blocks, 256, 0, st>>>(d, o_offset, lse_offset, parts->world, o_out, lse_out, total_rows, my_flags, slot, epoch, status, lim);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
 }
@@ -314,6 +344,7 @@ int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_d
   if ((offset & 15u) || (n & 3u)) return fail(LVX_ERR_ALIGN, "%s: offset must be a multiple of 16 bytes and n of 4 floats", who);
   if (out_dtype != LVX_BF16 && out_dtype != LVX_FP16 && out_dtype != LVX_FP32) return fail(LVX_ERR_DTYPE, "%s: dtype %d unsupported", who, out_dtype);
   if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  if ((rc = range_ok(parts, offset, n * sizeof(float), who, "the partial"))) return rc;
   int* status = device_status_ptr();
   if (!status) return fail(LVX_ERR_DRIVER, "%s: no device status word", who);
   if (n == 0) return LVX_OK;
@@ -321,9 +352,10 @@ int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_d
   const PeerPtrs d = to_dev(parts);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int g = grid_for(n4);
-  if (out_dtype == LVX_BF16) p2p_sum_cast_kernel<0><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status);
-  else if (out_dtype == LVX_FP16) p2p_sum_cast_kernel<1><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status);
-  else p2p_sum_cast_kernel<2><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status);
+  const long long lim = wait_limit_cycles();
+  if (out_dtype == LVX_BF16) p2p_sum_cast_kernel<0><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status, lim);
+  else if (out_dtype == LVX_FP16) p2p_sum_cast_kernel<1><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status, lim);
+  else p2p_sum_cast_kernel<2><<<g, 256, 0, st>>>(d, offset, parts->world, out, n4, my_flags, slot, epoch, status, lim);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
 }
@@ -337,6 +369,7 @@ int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_se
   if (flags->world != dst->world || flags->rank != dst->rank) return fail(LVX_ERR_SHAPE, "%s: the two peer tables disagree", who);
   if (!segments || nseg < 1 || nseg > LVX_P2P_MAX_SEGMENTS) return fail(LVX_ERR_SHAPE, "%s: 1..%d segments", who, LVX_P2P_MAX_SEGMENTS);
   if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  if ((rc = range_ok(flags, 0, sizeof(uint32_t) * LVX_P2P_SLOTS * LVX_MAX_PEERS, who, "the flag array"))) return rc;
   PushArgs a;
   a.nseg = nseg;
   size_t most = 0;
@@ -346,6 +379,11 @@ int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_se
     if ((reinterpret_cast<uintptr_t>(u.src) & 15u) || (u.src_stride & 15u) || (u.dst_offset & 15u) || (u.dst_rank_stride & 15u) ||
         (u.bytes & 15u))
       return fail(LVX_ERR_ALIGN, "%s: segment %d: addresses, strides and sizes must be multiples of 16 bytes", who, g);
+    // every rank writes at dst_offset + rank*dst_rank_stride: the last rank's block must still fit
+    if ((rc = range_ok(dst, u.dst_offset + size_t(dst->world - 1) * u.dst_rank_stride, u.bytes, who, "a segment's destination")))
+      return rc;
+    if (u.src_bytes && (u.src_stride ? size_t(dst->world - 1) * u.src_stride + u.bytes : u.bytes) > u.src_bytes)
+      return fail(LVX_ERR_LIMIT, "%s: segment %d reads past its %zu-byte source", who, g, size_t(u.src_bytes));
     a.seg[g].src = static_cast<const uint8_t*>(u.src);
     a.seg[g].src_stride = u.src_stride;
     a.seg[g].dst_offset = u.dst_offset;
@@ -366,9 +404,17 @@ int lvx_p2p_wait(const uint32_t* my_flags, int world, int slot, uint32_t epoch, 
   if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
   int* status = device_status_ptr();
   if (!status) return fail(LVX_ERR_DRIVER, "%s: no device status word", who);
-  p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, world, slot, epoch, status);
+  p2p_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(my_flags, world, slot, epoch, status,
+                                                                   wait_limit_cycles());
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
+}
+
+int lvx_p2p_set_timeout(double seconds) {
+  if (!(seconds > 0.0) || seconds > 86400.0)
+    return fail(LVX_ERR_SHAPE, "lvx_p2p_set_timeout: %g s is outside (0, 86400]", seconds);
+  g_wait_seconds = seconds;
+  return LVX_OK;
 }
 
 }  // extern "C"

@@ -65,7 +65,9 @@ def patch_cross_attention_forward(attention_mode="lv_xattn"):
             raise NotImplementedError("attention weights are never materialised by the flash kernels")
         if past_key_values is not None or past_key_value is not None:
             raise NotImplementedError("KV caching is a decoding feature; this hook is the training path")
-        if cross_attention_states is not None and get_global_cross_attention_states() is None:
+        if cross_attention_states is not None and cross_attention_states is not get_global_cross_attention_states():
+            # states handed to the call always win (the model passes fresh ones on every forward, reference
+            # test_llama3.py:540); valid lengths registered for other states do not carry over
             set_global_cross_attention_states(cross_attention_states, None)
         if get_global_cross_attention_states() is None:
             raise ValueError("no cross-attention states: pass them or call set_global_cross_attention_states")
@@ -82,8 +84,11 @@ def patch_cross_attention_forward(attention_mode="lv_xattn"):
 
         params = [p for p in (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.q_norm.weight,
                               self.k_norm.weight)]
-        attn = LVXAttnRecomputeFunc.apply(hidden_states, project, False, get_global_cross_attention_states,
-                                          _GLOBAL_KV_VALID_LEN, *params)
+        # the states of THIS call are bound here: a second forward with other states before this call's backward
+        # must not change what the recompute projects
+        states_now = get_global_cross_attention_states()
+        attn = LVXAttnRecomputeFunc.apply(hidden_states, project, False, lambda: states_now, _GLOBAL_KV_VALID_LEN,
+                                          *params)
         attn = attn.transpose(1, 2).reshape(bsz, q_len, nh * hd).contiguous()
         return self.o_proj(attn), None
 

@@ -301,6 +301,7 @@ def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int):
         arr[i].dst_offset = dst_offset
         arr[i].dst_rank_stride = dst_rank_stride
         arr[i].bytes = nbytes
+        arr[i].src_bytes = total
     _lib.check(lib.lvx_p2p_push(ctypes.byref(dst_peers), ctypes.byref(flags_peers), arr, len(segments), slot,
                                 ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()), "lvx_p2p_push")
     _count()

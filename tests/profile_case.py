@@ -1,17 +1,19 @@
 """Runs the forward and backward block kernels once (or a few times) on a synthetic bf16 case and prints their
 event-timed durations -- the small, self-ending workload to put under `ncu`.
 
-    python -m lv_xattn_b200.profile_case SQ SKV [ITERS] [B HQ HKV]
+    python tests/profile_case.py SQ SKV [ITERS] [B HQ HKV]
 
 Example (K/V = 128 MB, larger than the 126 MB L2; about 1 GB on the device):
-    ncu --set full --clock-control none -k regex:bwd_kernel -c 1 -o prof python -m lv_xattn_b200.profile_case 2048 32768
+    ncu --set full --clock-control none -k regex:bwd_kernel -c 1 -o prof python tests/profile_case.py 2048 32768
 """
 import math
+import os
 import sys
 
 import torch
 
-from . import _lib, ops
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from lv_xattn_b200 import _lib, ops  # noqa: E402
 
 
 def main(argv):

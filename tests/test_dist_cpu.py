@@ -167,3 +167,54 @@ def test_hf_hooks_sharded_over_two_ranks():
     mp.spawn(_hf_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     for r in range(2):
         assert ret.get(r, ("missing",))[0] == "ok", f"rank {r}: {ret.get(r)}"
+
+
+def _late_worker(rank, world, port, ret):
+    """Rank 1 shows up three seconds late; rank 0's wait is limited to one second."""
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    import time
+    import _stub_ops
+    import lv_xattn_b200.attn as attn
+    from lv_xattn_b200 import async_communication as ac
+    from oracle import attention_oracle as orc
+    attn.ops = _stub_ops
+    ac.P2P_TIMEOUT_S = 1.0
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ac.initialize_distributed()
+    q, k, v, _ = orc.make_inputs(1, 2, 2, 16 * world, 32 * world, 128, 5, torch.float32)
+    ql, kl, vl = (orc.shard(t, rank, world) for t in (q, k, v))
+    try:
+        if rank == 1:
+            time.sleep(3.0)                       # a stalled rank: host-side fault injection only
+        t0 = time.perf_counter()
+        attn._attn_forward(ql, kl, vl, False, SCALE, None, schedule="ring")
+        ret[rank] = ("returned", time.perf_counter() - t0)
+    except ac.P2PTimeoutError as e:
+        ret[rank] = ("timeout", time.perf_counter() - t0, str(e))
+    except Exception as e:  # the late rank may find its peer gone; any error is acceptable for it
+        ret[rank] = ("error", type(e).__name__)
+    os._exit(0)           # the process group may be wedged by the abandoned transfer: do not try to tear it down
+
+
+def test_stalled_peer_raises_p2p_timeout():
+    """A peer that does not deliver within LVX_P2P_TIMEOUT_S surfaces as P2PTimeoutError on the waiting rank,
+    instead of blocking for ever as the reference's wait_async_handles does (async_communication.py:301-305)."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    ctx = mp.get_context("spawn")
+    port = _free_port()
+    procs = [ctx.Process(target=_late_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p_ in procs:
+        p_.start()
+    for p_ in procs:
+        p_.join(60)
+    for p_ in procs:
+        if p_.is_alive():
+            p_.kill()
+            p_.join()
+    assert ret.get(0, ("missing",))[0] == "timeout", dict(ret)
+    assert 0.9 <= ret[0][1] <= 2.9, ret[0]          # gave up after about one second, well before rank 1 arrived
+    assert "P2P wait exceeded" in ret[0][2]

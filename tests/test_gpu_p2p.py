@@ -13,6 +13,7 @@ def _peers(tensors, rank):
     from lv_xattn_b200 import _lib
     p = _lib.LvxPeers()
     p.world, p.rank = len(tensors), rank
+    p.nbytes = min(t.numel() * t.element_size() for t in tensors)
     for i, t in enumerate(tensors):
         p.ptr[i] = t.data_ptr()
     return p
@@ -117,3 +118,64 @@ def test_argument_checks(dev):
     dst = torch.zeros(1, 24, dtype=torch.uint8, device=dev)
     with pytest.raises(_lib.LvxError):
         ops.p2p_gather(p, 0, 24, dst, flags, 0, 1)           # not a multiple of 16 bytes
+
+
+def test_bounds_checks_against_the_peer_buffer_size(dev):
+    """Offsets and extents are checked on the host against lvx_peers.nbytes before anything is launched."""
+    from lv_xattn_b200 import _lib, ops
+    flags = torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=dev)
+    bufs = [torch.zeros(4096, dtype=torch.uint8, device=dev) for _ in range(2)]
+    p = _peers(bufs, 0)
+    dst = torch.zeros(2, 4096, dtype=torch.uint8, device=dev)
+    with pytest.raises(_lib.LvxError, match="runs past"):
+        ops.p2p_gather(p, 16, 4096, dst, flags, 0, 1)                        # source range ends 16 bytes too far
+    out = torch.empty(1, 1, 8, 128, dtype=torch.float32, device=dev)
+    with pytest.raises(_lib.LvxError, match="runs past"):
+        ops.p2p_sum_cast(p, 2048, out, flags, 2, 1)                          # 4 KiB partial at offset 2 KiB
+    src = torch.zeros(2, 4096, dtype=torch.uint8, device=dev)
+    with pytest.raises(_lib.LvxError, match="runs past"):
+        ops.p2p_push(p, _peers([flags, flags], 0), [(src, True, 0, 4096)], 5, 1)   # rank 1's block lands at 4096
+    p.nbytes = 0
+    with pytest.raises(_lib.LvxError, match="no buffer size"):
+        ops.p2p_gather(p, 0, 16, torch.zeros(2, 16, dtype=torch.uint8, device=dev), flags, 0, 1)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+
+
+def test_wait_for_a_peer_that_never_signals_gives_up_cleanly(dev):
+    """A flag that nothing sets: with the limit lowered to a millisecond the wait kernel gives up, records
+    0x1300 | peer in the status word and returns -- nothing faults or hangs. While the word is set the library's
+    kernels return at once; reading the word clears it and the next call works again. The host-side watch turns
+    the word into P2PTimeoutError."""
+    import lv_xattn_b200 as lvx
+    from lv_xattn_b200 import _lib, ops, peer_memory as pm
+    lib = _lib.load()
+    world = 4
+    flags = torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=dev)
+    flags.view(_lib.P2P_SLOTS, _lib.MAX_PEERS)[6, :2] = 1                  # ranks 0 and 1 signalled epoch 1; 2 and 3 never do
+    torch.cuda.synchronize()
+    assert lib.lvx_p2p_set_timeout(ctypes.c_double(0.0)) != 0               # refused: must be positive
+    try:
+        _lib.check(lib.lvx_p2p_set_timeout(ctypes.c_double(1e-3)), "lvx_p2p_set_timeout")
+        ops.p2p_wait(flags, world, 6, 1)
+        # a kernel launched while the word is set returns without writing anything
+        a = torch.ones(1024, device=dev)
+        out = torch.full((1024,), 7.0, device=dev)
+        ops.add_cast(a, None, torch.float32, out=out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, torch.full((1024,), 7.0, device=dev))
+        pm.status_watch.post()
+        with pytest.raises(lvx.P2PTimeoutError, match="rank 2"):
+            pm.status_watch.check()
+        assert _lib.device_status() == 0                                    # the watch cleared the word
+        ops.add_cast(a, None, torch.float32, out=out)                       # and the library works again
+        torch.cuda.synchronize()
+        assert torch.equal(out, a)
+        # same through the raw status call
+        ops.p2p_wait(flags, world, 6, 1)
+        torch.cuda.synchronize()
+        assert _lib.device_status() == (0x1300 | 2)
+        assert _lib.device_status() == 0
+    finally:
+        _lib.check(lib.lvx_p2p_set_timeout(ctypes.c_double(120.0)), "lvx_p2p_set_timeout")
+        _lib.device_status()

@@ -50,6 +50,37 @@ def test_cross_attention_hook_matches_stock_module(monkeypatch):
         assert torch.allclose(a, b, atol=5e-5, rtol=1e-3), (name, (a - b).abs().max())
 
 
+def test_cross_attention_hook_uses_the_states_of_each_call(monkeypatch):
+    """Two forwards with different visual states passed as arguments (the normal Hugging Face call path), both
+    before any backward: each output and each backward must belong to its own states."""
+    import _stub_ops
+    import lv_xattn_b200.attn as attn
+    from lv_xattn_b200 import hf_patch
+    monkeypatch.setattr(attn, "ops", _stub_ops)
+    cfg, cross, _, _ = make_modules()
+    patched = copy.deepcopy(cross)
+    patched.forward = hf_patch.patch_cross_attention_forward("lv_xattn").__get__(patched)
+    hf_patch.clear_global_cross_attention_states()
+    x = torch.randn(1, 12, 256)
+    st_a, st_b = torch.randn(1, 40, 256), torch.randn(1, 56, 256)
+    try:
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        out_a, _ = patched(xa, cross_attention_states=st_a)
+        out_b, _ = patched(xb, cross_attention_states=st_b)          # second batch: new states
+        g = torch.randn_like(out_a)
+        out_a.backward(g)                                            # recompute must still see st_a
+        out_b.backward(g)
+    finally:
+        hf_patch.clear_global_cross_attention_states()
+    for st, out, xg in ((st_a, out_a, xa.grad), (st_b, out_b, xb.grad)):
+        xr = x.clone().requires_grad_(True)
+        ref, _ = cross(xr, cross_attention_states=st)
+        ref.backward(g)
+        assert torch.allclose(out, ref, atol=2e-5, rtol=1e-4)
+        assert torch.allclose(xg, xr.grad, atol=5e-5, rtol=1e-3)
+    assert not torch.allclose(out_a, out_b, atol=1e-3)
+
+
 def test_self_attention_hook_matches_stock_module_single_rank():
     from lv_xattn_b200 import hf_patch
     cfg, _, selfa, rope = make_modules()

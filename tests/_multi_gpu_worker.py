@@ -58,5 +58,56 @@ for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
             _parity.assert_fp32(got[name], ref[name], name, label)
         else:
             _parity.assert_close(got[name], ref[name], name, label, *_parity.BF16[name])
+
+# ---- the two Hugging Face hooks on GPU ranks: sharded text and visual sequences against the unsharded stock modules
+try:
+    from transformers.models.mllama import modeling_mllama as mllama
+except ImportError:
+    mllama = None
+if mllama is not None and "hf" in sys.argv[2:]:
+    import copy
+    from lv_xattn_b200 import hf_patch
+    cfg = mllama.MllamaTextConfig(hidden_size=512, num_attention_heads=4, num_key_value_heads=2,
+                                  num_hidden_layers=2, intermediate_size=512, vocab_size=64)
+    cfg._attn_implementation = "eager"
+    torch.manual_seed(0)                                      # the same weights and inputs on every rank
+    cross = mllama.MllamaTextCrossAttention(cfg, layer_idx=0).to(dev)
+    selfa = mllama.MllamaTextSelfAttention(cfg, layer_idx=1).to(dev)
+    rope = mllama.MllamaRotaryEmbedding(cfg).to(dev)
+    S, Skv = 64 * world, 1601 * world                          # per-rank K/V length not a multiple of 128
+    x = torch.randn(1, S, 512, device=dev)
+    states = torch.randn(1, Skv, 512, device=dev)
+    g = torch.randn(1, S, 512, device=dev)
+    cos, sin = rope(x, torch.arange(S, device=dev)[None])
+    causal = torch.full((S, S), float("-inf"), device=dev).triu(1)[None, None]
+    xr = x.clone().requires_grad_(True)
+    ref_c, _ = cross(xr, cross_attention_states=states)
+    ref_s, _ = selfa(xr, attention_mask=causal, position_embeddings=(cos, sin))
+    (ref_c + ref_s).backward(g)
+    n, m = S // world, Skv // world
+    sl = slice(rank * n, (rank + 1) * n)
+    pc, ps = copy.deepcopy(cross).to(torch.bfloat16), copy.deepcopy(selfa).to(torch.bfloat16)
+    for p_ in list(pc.parameters()) + list(ps.parameters()):
+        p_.grad = None
+    pc.forward = hf_patch.patch_cross_attention_forward("lv_xattn").__get__(pc)
+    ps.forward = hf_patch.patch_self_attention_forward("lv_xattn").__get__(ps)
+    xl = x[:, sl].to(torch.bfloat16).requires_grad_(True)
+    hf_patch.set_global_cross_attention_states(states[:, rank * m:(rank + 1) * m].to(torch.bfloat16).contiguous())
+    out_c, _ = pc(xl)
+    out_s, _ = ps(xl, attention_mask=None,                      # this rank's slice of the rotary tables
+                  position_embeddings=(cos[:, sl].to(torch.bfloat16), sin[:, sl].to(torch.bfloat16)))
+    (out_c + out_s).backward(g[:, sl].to(torch.bfloat16))
+    hf_patch.clear_global_cross_attention_states()
+
+    def rel(a, b):
+        return ((a.float() - b).norm() / b.norm()).item()
+
+    assert rel(out_c, ref_c[:, sl]) <= 2e-2 and rel(out_s, ref_s[:, sl]) <= 2e-2, (rel(out_c, ref_c[:, sl]), rel(out_s, ref_s[:, sl]))
+    assert rel(xl.grad, xr.grad[:, sl]) <= 3e-2, rel(xl.grad, xr.grad[:, sl])
+    for (name, p_), (_, pr) in zip(list(pc.named_parameters()) + list(ps.named_parameters()),
+                                   list(cross.named_parameters()) + list(selfa.named_parameters())):
+        gsum = p_.grad.float().clone()                          # weight gradients are partial sums per rank
+        torch.distributed.all_reduce(gsum)
+        assert rel(gsum, pr.grad) <= 3e-2, (name, rel(gsum, pr.grad))
 print(f"RANK_OK {rank}", flush=True)
 torch.distributed.destroy_process_group()

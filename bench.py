@@ -472,6 +472,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="K/V chunks of the host-streamed end-to-end step")
+    ap.add_argument("--attention", default="lv_xattn", choices=["lv_xattn", "ring"],
+                    help="lv_xattn: the query side rotates, K/V resident (the product path); ring: the K/V-rotating "
+                         "ring-attention baseline on the same kernels (reference ring/attn.py), for comparison")
+    ap.add_argument("--schedule", default=None, help="LV-XAttn exchange schedule (default: LVX_SCHEDULE or auto)")
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.impl == "reference":
@@ -514,9 +518,16 @@ def main():
     flops_step = f_fwd + f_bwd
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
+    if args.attention == "ring":
+        from lv_xattn_b200 import ring as impl
+        sched_kw = {}
+    else:
+        impl = lvx
+        sched_kw = {"schedule": args.schedule} if args.schedule else {}
+
     def step_device():
-        _, _, _, o, L = lvx._attn_forward(q, k, v, False, scale, None, kv_valid_len=valid)
-        return lvx._attn_backward(do, q, k, v, o, L, False, scale, None, "flash", kv_valid_len=valid) + (o, L)
+        _, _, _, o, L = impl._attn_forward(q, k, v, False, scale, None, kv_valid_len=valid, **sched_kw)
+        return impl._attn_backward(do, q, k, v, o, L, False, scale, None, "flash", kv_valid_len=valid, **sched_kw) + (o, L)
 
     def barrier():
         if world > 1:
@@ -613,7 +624,7 @@ def main():
 
     # ---- end-to-end run: host (pinned) inputs, results read back ------------------------------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and args.attention == "lv_xattn":
         hq, hk, hv, hdo = (t.cpu().pin_memory() for t in (q, k, v, do))
         ho, hdq = torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory()
         hdk, hdv = torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()
@@ -644,7 +655,9 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": cfg["dtype"], "data": "synthetic",
             "config": {"workload": workload_name(args.config, cfg), "l2": "256 MB buffer written between timed steps",
-                       "schedule": "single GPU" if world == 1 else lvx.attn._schedule(None, q),
+                       "schedule": "single GPU" if world == 1 else (
+                           "ring attention baseline (K/V rotate over NCCL P2P)" if args.attention == "ring"
+                           else lvx.attn._schedule(args.schedule, q)),
                        "timing": "CUDA events per step on the launch stream, summed; max over ranks"},
             "ms_per_layer": ms_per_step, "tflops_per_gpu": value / world,
             "frac_of_tensor_roofline": (roof_job * 1e3) / ms_per_step, "wall_ms": wall_ms,

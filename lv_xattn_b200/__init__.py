@@ -15,6 +15,7 @@ from .async_communication import (  # noqa: F401
 from .attn import (  # noqa: F401
     LVXAttnFunc,
     LVXAttnRecomputeFunc,
+    RingAttnRecomputeFunc,
     _attn_backward,
     _attn_forward,
     attention,

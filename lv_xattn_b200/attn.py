@@ -478,54 +478,79 @@ class LVXAttnFunc(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None, None, None
 
 
-class LVXAttnRecomputeFunc(torch.autograd.Function):
-    """attention(x, run_function, is_causal, *params) -> o, where run_function(x, states) -> (q, k, v) is the
-    projection of the layer and `states` are the visual features held in a module global
-    (see hf_patch.set_global_cross_attention_states). Only (x, o, L) are saved: K/V are recomputed in
+def _make_recompute_class(name, fwd, bwd, doc):
+    """The recompute-QKV wrapper over a given pair of step-loop functions (LV-XAttn or the ring baseline)."""
+
+    class _Recompute(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x, run_function, is_causal, states_getter, kv_valid_len, *params):
+            with torch.no_grad():
+                q, k, v = run_function(x, states_getter())
+            sm_scale = q.shape[-1] ** -0.5
+            _, _, _, o, L = fwd()(q, k, v, is_causal, sm_scale, None, kv_valid_len=kv_valid_len)
+            ctx.save_for_backward(x, o, L, *params)
+            ctx.run_function = run_function
+            ctx.states_getter = states_getter
+            ctx.is_causal = is_causal
+            ctx.sm_scale = sm_scale
+            ctx.kv_valid_len = kv_valid_len
+            del q, k, v
+            return o
+
+        @staticmethod
+        def backward(ctx, do):
+            x, o, L, *params = ctx.saved_tensors
+            with torch.enable_grad():
+                x_ = x.detach().requires_grad_(x.requires_grad)
+                q, k, v = ctx.run_function(x_, ctx.states_getter())
+            dq, dk, dv = bwd()(do, q.detach(), k.detach(), v.detach(), o, L, ctx.is_causal, ctx.sm_scale, None, "flash",
+                               kv_valid_len=ctx.kv_valid_len)
+            inputs = [t for t in ([x_] + list(params)) if t.requires_grad]
+            grads = torch.autograd.grad((q, k, v), inputs, (dq, dk, dv), allow_unused=True) if inputs else ()
+            it = iter(grads)
+            gx = next(it) if x_.requires_grad else None
+            gparams = [next(it) if p.requires_grad else None for p in params]
+            return (gx, None, None, None, None, *gparams)
+
+    _Recompute.__name__ = _Recompute.__qualname__ = name
+    _Recompute.__doc__ = doc
+    return _Recompute
+
+
+LVXAttnRecomputeFunc = _make_recompute_class(
+    "LVXAttnRecomputeFunc", lambda: _attn_forward, lambda: _attn_backward,
+    """attention(x, run_function, is_causal, states_getter, kv_valid_len, *params) -> o, where
+    run_function(x, states) -> (q, k, v) is the projection of the layer and `states` are the visual features held in a
+    module global (see hf_patch.set_global_cross_attention_states). Only (x, o, L) are saved: K/V are recomputed in
     backward, which keeps the per-layer activation memory independent of the visual sequence length
     (reference test_llama3.py:180-245). Unlike the reference (:243 returns None for every input), backward
     re-runs the projection under autograd and propagates dq, dk, dv into x and into `params` (the tensors
-    run_function closes over, passed so that autograd sees them)."""
+    run_function closes over, passed so that autograd sees them).""")
 
-    @staticmethod
-    def forward(ctx, x, run_function, is_causal, states_getter, kv_valid_len, *params):
-        with torch.no_grad():
-            q, k, v = run_function(x, states_getter())
-        sm_scale = q.shape[-1] ** -0.5
-        _, _, _, o, L = _attn_forward(q, k, v, is_causal, sm_scale, None, kv_valid_len=kv_valid_len)
-        ctx.save_for_backward(x, o, L, *params)
-        ctx.run_function = run_function
-        ctx.states_getter = states_getter
-        ctx.is_causal = is_causal
-        ctx.sm_scale = sm_scale
-        ctx.kv_valid_len = kv_valid_len
-        del q, k, v
-        return o
 
-    @staticmethod
-    def backward(ctx, do):
-        x, o, L, *params = ctx.saved_tensors
-        with torch.enable_grad():
-            x_ = x.detach().requires_grad_(x.requires_grad)
-            q, k, v = ctx.run_function(x_, ctx.states_getter())
-        dq, dk, dv = _attn_backward(do, q.detach(), k.detach(), v.detach(), o, L, ctx.is_causal, ctx.sm_scale,
-                                    None, "flash", kv_valid_len=ctx.kv_valid_len)
-        inputs = [t for t in ([x_] + list(params)) if t.requires_grad]
-        grads = torch.autograd.grad((q, k, v), inputs, (dq, dk, dv), allow_unused=True) if inputs else ()
-        it = iter(grads)
-        gx = next(it) if x_.requires_grad else None
-        gparams = [next(it) if p.requires_grad else None for p in params]
-        return (gx, None, None, None, None, *gparams)
+def _ring():
+    from . import ring
+    return ring
+
+
+RingAttnRecomputeFunc = _make_recompute_class(
+    "RingAttnRecomputeFunc", lambda: _ring()._attn_forward, lambda: _ring()._attn_backward,
+    """The same recompute-QKV wrapper over the ring (K/V-rotating) baseline, lv_xattn_b200.ring
+    (reference test_llama3.py:180-245 with attention_mode="ring").""")
 
 
 def create_attention_class(attention_mode="lv_xattn"):
-    """Same factory as reference test.py:38: returns the autograd class for `attention_mode`."""
-    if attention_mode != "lv_xattn":
-        raise NotImplementedError(f"attention_mode {attention_mode!r}: only 'lv_xattn' is built")
-    return LVXAttnFunc
+    """Same factory as reference test.py:38: returns the autograd class for `attention_mode`
+    ("lv_xattn", or "ring" for the K/V-rotating baseline on the same kernels)."""
+    if attention_mode == "lv_xattn":
+        return LVXAttnFunc
+    if attention_mode in ("ring", "ring_self"):
+        return _ring().RingAttnFunc
+    raise NotImplementedError(f"attention_mode {attention_mode!r}: expected 'lv_xattn' or 'ring'")
 
 
 attention = LVXAttnFunc.apply
 
-__all__ = ["_attn_forward", "_attn_backward", "LVXAttnFunc", "LVXAttnRecomputeFunc", "create_attention_class",
+__all__ = ["_attn_forward", "_attn_backward", "LVXAttnFunc", "LVXAttnRecomputeFunc", "RingAttnRecomputeFunc",
+           "create_attention_class",
            "attention", "reset_global_memory_buffer"]

@@ -25,9 +25,9 @@ import torch
 import torch.distributed as dist
 
 from .async_communication import get_sequence_parallel_group, get_sequence_parallel_rank, get_sequence_parallel_size
-from .attn import LVXAttnRecomputeFunc
+from .attn import LVXAttnRecomputeFunc, RingAttnRecomputeFunc
 
-ATTENTION_MODES = ("lv_xattn",)
+ATTENTION_MODES = ("lv_xattn", "ring", "ring_self")      # the reference's modes (test_llama3.py:107)
 
 _GLOBAL_CROSS_ATTENTION_STATES = None
 _GLOBAL_KV_VALID_LEN = None
@@ -51,13 +51,15 @@ def clear_global_cross_attention_states():
 
 def _check_mode(attention_mode):
     if attention_mode not in ATTENTION_MODES:
-        raise NotImplementedError(f"attention_mode {attention_mode!r}: only 'lv_xattn' is built "
-                                  "(the reference's 'ring' / 'ring_self' baselines are out of scope)")
+        raise NotImplementedError(f"attention_mode {attention_mode!r}: expected one of {ATTENTION_MODES}")
 
 
 def patch_cross_attention_forward(attention_mode="lv_xattn"):
-    """Returns an unbound `forward` for `MllamaTextCrossAttention` (reference test_llama3.py:356-468)."""
+    """Returns an unbound `forward` for `MllamaTextCrossAttention` (reference test_llama3.py:356-468).
+    attention_mode "lv_xattn" rotates the query side (K/V resident); "ring" / "ring_self" run the K/V-rotating
+    baseline (lv_xattn_b200.ring) on the same kernels."""
     _check_mode(attention_mode)
+    recompute = LVXAttnRecomputeFunc if attention_mode == "lv_xattn" else RingAttnRecomputeFunc
 
     def forward(self, hidden_states, cross_attention_states=None, past_key_values=None, attention_mask=None,
                 output_attentions=False, use_cache=None, cache_position=None, past_key_value=None, **kwargs):
@@ -87,8 +89,7 @@ def patch_cross_attention_forward(attention_mode="lv_xattn"):
         # the states of THIS call are bound here: a second forward with other states before this call's backward
         # must not change what the recompute projects
         states_now = get_global_cross_attention_states()
-        attn = LVXAttnRecomputeFunc.apply(hidden_states, project, False, lambda: states_now, _GLOBAL_KV_VALID_LEN,
-                                          *params)
+        attn = recompute.apply(hidden_states, project, False, lambda: states_now, _GLOBAL_KV_VALID_LEN, *params)
         attn = attn.transpose(1, 2).reshape(bsz, q_len, nh * hd).contiguous()
         return self.o_proj(attn), None
 
@@ -122,7 +123,9 @@ def patch_self_attention_forward(attention_mode="lv_xattn"):
     self-attention layers gather K/V over the sequence-parallel group and apply the causal mask with global
     positions (query row i of rank r sits at position r*S_local + i). `position_embeddings` must already be
     this rank's slice of the rotary tables. The attention itself is torch's scaled_dot_product_attention: the
-    self-attention layers are not the path this library accelerates."""
+    self-attention layers are not the path this library accelerates. Every attention_mode gets this
+    implementation: the reference's "ring_self" applies its causal mask with rank-local indices at every step
+    (ring/attn.py:280), which is not globally correct, so it is not reproduced."""
     _check_mode(attention_mode)
 
     def forward(self, hidden_states, attention_mask=None, position_embeddings=None, output_attentions=False,

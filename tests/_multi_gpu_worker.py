@@ -32,9 +32,14 @@ for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
     ql, dol, kl, vl = (orc.shard(t, rank, world).to(dev) for t in (q, do, k, v))
     torch.distributed.barrier()          # the oracle above takes a different time on every rank
     for rep, sched in enumerate(schedules):
-        _, _, _, o, L = lvx._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid, schedule=sched)
-        dq, dk, dv = lvx._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid,
-                                        schedule=sched)
+        if sched == "kvring":       # the K/V-rotating ring baseline on the same kernels (lv_xattn_b200.ring)
+            from lv_xattn_b200 import ring
+            _, _, _, o, L = ring._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid)
+            dq, dk, dv = ring._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid)
+        else:
+            _, _, _, o, L = lvx._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid, schedule=sched)
+            dq, dk, dv = lvx._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid,
+                                            schedule=sched)
         if rep == 0:
             first = [t.clone() for t in (o, L, dq, dk, dv)]
         for name, a, b in zip(("o", "lse", "dq", "dk", "dv"), first, (o, L, dq, dk, dv)):   # every schedule computes the same thing

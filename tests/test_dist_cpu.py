@@ -39,10 +39,16 @@ def _worker(rank, world, port, case, ret):
         o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, SCALE, kv_valid)
         ql, dol = orc.shard(q, rank, world), orc.shard(do, rank, world)
         kl, vl = orc.shard(k, rank, world), orc.shard(v, rank, world)
+        kw = dict(kw)
+        mod = attn
+        if kw.pop("baseline", None) == "ring":      # the K/V-rotating baseline on the same (stubbed) kernels
+            from lv_xattn_b200 import ring
+            ring.ops = _stub_ops
+            mod = ring
         for rep in range(2):   # twice: pooled slabs are reused
-            _, _, _, o, L = attn._attn_forward(ql, kl, vl, False, SCALE, None, kv_valid_len=kv_valid, **kw)
-            dq, dk, dv = attn._attn_backward(dol, ql, kl, vl, o, L, False, SCALE, None, "flash",
-                                             kv_valid_len=kv_valid, **kw)
+            _, _, _, o, L = mod._attn_forward(ql, kl, vl, False, SCALE, None, kv_valid_len=kv_valid, **kw)
+            dq, dk, dv = mod._attn_backward(dol, ql, kl, vl, o, L, False, SCALE, None, "flash",
+                                            kv_valid_len=kv_valid, **kw)
         tol = 1e-4 if dtype == torch.float32 else 3e-2
         Sl = Sq // world
         lse_l = orc.shard(lse_ref.unsqueeze(-1), rank, world).squeeze(-1)
@@ -88,6 +94,17 @@ def test_step_loop_bf16_gqa_key_padding():
     # per-sample valid lengths: one sample ends inside rank 1's shard, one has nothing beyond rank 0
     _run(4, (2, 4, 1, 32, 256, torch.bfloat16, [200, 40], {}))
     _run(4, (2, 4, 1, 32, 256, torch.bfloat16, [200, 40], {"schedule": "ring"}))
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4])
+def test_ring_baseline_fp32(world):
+    """lv_xattn_b200.ring (K/V rotate, dK/dV accumulators travel) against the full-tensor oracle."""
+    _run(world, (1, 4, 2, 24 * world, 64 * world, torch.float32, None, {"baseline": "ring"}))
+
+
+def test_ring_baseline_bf16_gqa_key_padding():
+    _run(4, (2, 4, 1, 32, 256, torch.bfloat16, [200, 40], {"baseline": "ring"}))
+    _run(2, (1, 2, 2, 32, 128, torch.float32, None, {"baseline": "ring", "no_overlap": True}))
 
 
 def test_step_loop_no_overlap():

@@ -25,7 +25,9 @@ def _run(world, schedules, port, extra=()):
 
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_ring_nccl(world):
-    _run(world, "gather,ring", 29600 + world)
+    """The NCCL schedules: all-blocks-per-pass ("gather"), the reference's Q-rotating step loop ("ring") and the
+    K/V-rotating ring-attention baseline ("kvring"), all against each other and the oracle."""
+    _run(world, "gather,ring,kvring", 29600 + world)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

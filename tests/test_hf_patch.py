@@ -95,9 +95,15 @@ def test_self_attention_hook_matches_stock_module_single_rank():
     assert torch.allclose(out, ref, atol=2e-5, rtol=1e-4)
 
 
-def test_unsupported_modes_raise():
-    from lv_xattn_b200 import hf_patch
+def test_attention_modes():
+    """The reference's three modes are accepted (test_llama3.py:107); anything else raises."""
+    import lv_xattn_b200 as lvx
+    from lv_xattn_b200 import hf_patch, ring
+    for mode in ("lv_xattn", "ring", "ring_self"):
+        assert callable(hf_patch.patch_cross_attention_forward(mode))
+        assert callable(hf_patch.patch_self_attention_forward(mode))
+    assert lvx.create_attention_class("ring") is ring.RingAttnFunc
     with pytest.raises(NotImplementedError):
-        hf_patch.patch_cross_attention_forward("ring")
+        hf_patch.patch_cross_attention_forward("ulysses")
     with pytest.raises(NotImplementedError):
-        hf_patch.patch_self_attention_forward("ring_self")
+        lvx.create_attention_class("ulysses")

@@ -120,6 +120,28 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
                   float* dk_acc, float* dv_acc, int accumulate_dkdv, void* workspace,
                   size_t workspace_bytes, void* stream);
 
+/* Dense additive bias on the scores, S = sm_scale * q.k + bias (natural-log domain, not scaled): the reference's
+ * bias_func protocol builds such a tensor for every step, lv_xattn/attn.py:386-389, and its kernels add it at
+ * lv_xattn/attn.py:238-240 (forward) and lv_xattn/flash_attn_kernels.py:497-516 (backward recompute). `bias` is fp32
+ * on the device; the value for (query block n, batch b, query head h, query row i, key j) is
+ * bias[n*stride_block + b*stride_b + h*stride_h + i*stride_q + j*stride_kv] (strides in floats, 0 = broadcast,
+ * e.g. stride_h = 0 for a [B,1,Sq,Skv] bias). -inf entries mask a key. No gradient is produced for the bias, as in
+ * the reference. */
+typedef struct lvx_bias {
+  const float* bias;
+  int64_t stride_block, stride_b, stride_h, stride_q, stride_kv;
+} lvx_bias;
+
+/* lvx_fwd_block / lvx_bwd_block with a dense bias (any dtype). These run the library's general FP32-FMA block
+ * kernels instead of the tensor-core ones (key padding expressed as kv_valid_len stays on the tensor-core path);
+ * same workspace, outputs and accumulate modes. */
+int lvx_fwd_block_bias(const lvx_shape* s, const void* q, const void* k, const void* v,
+                       const int32_t* kv_valid_len, const lvx_bias* bias, float sm_scale, void* workspace,
+                       size_t workspace_bytes, void* stream);
+int lvx_bwd_block_bias(const lvx_shape* s, const void* q, const void* d_o, const float* lse, const float* delta,
+                       const void* k, const void* v, const int32_t* kv_valid_len, const lvx_bias* bias,
+                       float sm_scale, float* dq_acc, void* dk_acc, void* dv_acc, int accumulate_dkdv, void* stream);
+
 /* Merge of `count` finished partial results of the same query block, each computed against a different
  * K/V shard: o_parts fp32 [count][B*Hq*Sq*D], lse_parts fp32 [count][B*Hq*Sq] -> o_out (shape.dtype) and
  * lse_out, with the same stable log-sum-exp merge as lvx_fwd_combine_merge ((0,-inf) is the neutral

@@ -19,7 +19,7 @@ _DTYPE = {torch.bfloat16: LVX_BF16, torch.float16: LVX_FP16, torch.float32: LVX_
 # every symbol include/lvx.h declares
 SYMBOLS = [
     "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_device_status_peek", "lvx_p2p_set_timeout",
-    "lvx_query_workspace", "lvx_fwd_block",
+    "lvx_query_workspace", "lvx_fwd_block", "lvx_fwd_block_bias", "lvx_bwd_block_bias",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
     "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
     "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast", "lvx_p2p_push", "lvx_p2p_wait",
@@ -35,6 +35,11 @@ class LvxShape(ctypes.Structure):
 class LvxPeers(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("ptr", ctypes.c_void_p * 16),
                 ("nbytes", ctypes.c_size_t)]
+
+
+class LvxBias(ctypes.Structure):
+    _fields_ = [("bias", ctypes.c_void_p)] + [(n, ctypes.c_int64) for n in
+                                               ("stride_block", "stride_b", "stride_h", "stride_q", "stride_kv")]
 
 
 class LvxPushSegment(ctypes.Structure):
@@ -68,6 +73,9 @@ def load():
     lib.lvx_p2p_set_timeout.argtypes = [ctypes.c_double]
     lib.lvx_query_workspace.argtypes = [sp, ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
     lib.lvx_fwd_block.argtypes = [sp, vp, vp, vp, i32p, ctypes.c_float, vp, ctypes.c_size_t, vp]
+    bp = ctypes.POINTER(LvxBias)
+    lib.lvx_fwd_block_bias.argtypes = [sp, vp, vp, vp, i32p, bp, ctypes.c_float, vp, ctypes.c_size_t, vp]
+    lib.lvx_bwd_block_bias.argtypes = [sp, vp, vp, fp, fp, vp, vp, i32p, bp, ctypes.c_float, fp, vp, vp, ctypes.c_int, vp]
     lib.lvx_fwd_combine_merge.argtypes = [sp, vp, fp, fp, vp, fp, ctypes.c_int, vp]
     lib.lvx_bwd_prep.argtypes = [sp, vp, vp, fp, vp]
     lib.lvx_bwd_block.argtypes = [sp, vp, vp, fp, fp, vp, vp, i32p, ctypes.c_float, fp, fp, fp, ctypes.c_int, vp,

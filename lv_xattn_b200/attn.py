@@ -15,7 +15,10 @@ Differences from the reference that are deliberate: the travelling accumulators 
 :448,:527), the empty accumulator is (0, -inf) instead of lse = 0 (:319), the result is taken from the slot
 that actually holds it for every W (reference returns slot 0, wrong for odd W, :435), delta is computed once
 at home and travels instead of O (:926-942 recomputes it on every rank), K/V are used at their own head
-count (no expansion, :392-393), and key padding is a per-batch valid length instead of a dense bias.
+count (no expansion, :392-393), and key padding has a native form (a per-batch valid length, handled inside the
+tensor-core kernels). The reference's general bias protocol -- bias_func(*local_bias_args, *remote_bias_args),
+the remote arguments travelling with the query block (:359-360, :373-374, :386-389) -- is kept: with a bias_func
+the step loop runs one block per step and the block kernels are the general FP32-FMA ones.
 """
 from __future__ import annotations
 
@@ -87,9 +90,8 @@ def _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args)
     if bias_func is None:
         if len(local_bias_args) or len(remote_bias_args):
             raise ValueError("bias arguments given without a bias_func")
-    else:
-        raise NotImplementedError(
-            "dense additive bias_func is not supported; key padding is expressed with kv_valid_len")
+    elif not callable(bias_func):
+        raise ValueError("bias_func must be callable: bias_func(*local_bias_args, *remote_bias_args) -> bias")
     if causal:
         raise NotImplementedError(
             "causal=True is not supported: cross-attention has no causal order, and the reference applies "
@@ -103,6 +105,19 @@ def _local_valid(kv_valid_len, skv_local: int, device):
     t = torch.as_tensor(kv_valid_len, device=device).to(torch.int64)
     t = (t - get_sequence_parallel_rank() * skv_local).clamp_(0, skv_local)
     return t.to(torch.int32).contiguous()
+
+
+def _build_bias(bias_func, local_bias_args, peer_bias_args, q, k):
+    """The reference's bias protocol (lv_xattn/attn.py:386-389): the additive bias of one step is
+    bias_func(*local_bias_args, *peer_bias_args) -> [B, 1 or H, Sq_local, Skv_local], where the local arguments
+    belong to this rank's K/V shard and the peer arguments arrived with the query block. It is added to the scaled
+    scores (S = sm_scale*q.k + bias); steps with a bias run the general FP32-FMA kernels."""
+    if bias_func is None:
+        return None
+    bias = bias_func(*(list(local_bias_args) + list(peer_bias_args)))
+    if not torch.is_tensor(bias) or bias.dim() != 4:
+        raise ValueError("bias_func must return a 4-D tensor broadcastable to [B, H, Sq, Skv]")
+    return bias.to(device=q.device, dtype=torch.float32)
 
 
 def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> torch.Tensor:
@@ -131,13 +146,15 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
     L = torch.empty(B * Hq, Sq, dtype=torch.float32, device=dev)
 
     if W == 1 or comm_mode == "nocomm":
+        bias = _build_bias(bias_func, local_bias_args, remote_bias_args, qc, kc)
         for _ in range(W):
-            part = ops.fwd_partials(qc, kc, vc, sm_scale, kvl)
+            part = ops.fwd_partials(qc, kc, vc, sm_scale, kvl, bias=bias)
             ops.fwd_combine(part, None, None, o, L, True)
         return q, k, v, o, L
 
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
-    sched = _schedule(schedule, q)
+    # a bias is built per step from arguments that travel with the query block: the step loop is the only schedule
+    sched = "ring" if bias_func is not None else _schedule(schedule, q)
     if sched in ("p2p", "p2p_pull") and (n_l * 4) % 16:
         if (schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)) != "auto":
             raise ValueError("the p2p schedules need B*Hq*Sq to be a multiple of 4")
@@ -223,6 +240,8 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         return o_v, l_v
 
     q_cur = qc
+    args_cur = [a.contiguous() for a in remote_bias_args] if bias_func is not None else []
+    args_bufs = [[torch.empty_like(a) for a in args_cur] for _ in range(2)]
     q_reqs, acc_reqs = [], []
     for t in range(W):
         last = t == W - 1
@@ -230,11 +249,13 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         q_reqs = []
         if not last:
             q_next = _carve(q_bufs[t % 2], 0, (B, Hq, Sq, D), dt)
-            q_reqs = send_recv_fwd_q(q_cur, q_next, [], [], comm_mode)
+            args_next = args_bufs[t % 2]
+            q_reqs = send_recv_fwd_q(q_cur, q_next, args_cur, args_next, comm_mode)
             if no_overlap:
                 wait_async_handles(q_reqs)
                 q_reqs = []
-        part = ops.fwd_partials(q_cur, kc, vc, sm_scale, kvl)
+        bias = _build_bias(bias_func, local_bias_args, args_cur, q_cur, kc)
+        part = ops.fwd_partials(q_cur, kc, vc, sm_scale, kvl, bias=bias)
         wait_async_handles(acc_reqs)        # travelling accumulator of this block (and last step's send)
         o_in = l_in = None
         if t > 0:
@@ -252,7 +273,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
             wait_async_handles(acc_reqs)
             acc_reqs = []
         if not last:
-            q_cur = q_next
+            q_cur, args_cur = q_next, args_next
     wait_async_handles(acc_reqs)
     return q, k, v, o, L
 
@@ -290,14 +311,15 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
     delta = ops.bwd_prep(oc, doc)                       # once, at home; travels instead of O
     dq = torch.empty(B, Hq, Sq, D, dtype=dt, device=dev)
 
-    sched = _schedule(schedule, q) if W > 1 else "gather"
+    sched = ("ring" if bias_func is not None else _schedule(schedule, q)) if W > 1 else "gather"
     if W == 1 or comm_mode == "nocomm":
         dq_acc = _carve(get_slabs("bwd_dq_delta", n_q * 4, dev, 1)[0], 0, (B, Hq, Sq, D), torch.float32)
         dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        bias = _build_bias(bias_func, local_bias_args, remote_bias_args, qc, kc)
         for t in range(W):
             dq_acc.zero_()
-            ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl)
+            ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl, bias=bias)
         ops.add_cast(dq_acc, None, dt, out=dq)
         return dq, dk, dv
     if sched in ("p2p", "p2p_pull") and (n_r * 4) % 16:
@@ -408,6 +430,8 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         cl.copy_(Lc)
         cd.copy_(delta)
         comp_reqs, dq_reqs = [], []
+        args_cur = [a.contiguous() for a in remote_bias_args] if bias_func is not None else []
+        args_bufs = [[torch.empty_like(a) for a in args_cur] for _ in range(2)]
         for t in range(W):
             last = t == W - 1
             wait_async_handles(comp_reqs)
@@ -415,7 +439,8 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             cq, cdo, cl, cd = slab_views(cur)
             if not last:
                 nxt = in_bufs[t % 2]
-                comp_reqs = send_recv_bwd_comp_reqs(cur[:slab_bytes], nxt[:slab_bytes], [], [], comm_mode)
+                args_next = args_bufs[t % 2]
+                comp_reqs = send_recv_bwd_comp_reqs(cur[:slab_bytes], nxt[:slab_bytes], args_cur, args_next, comm_mode)
                 if no_overlap:
                     wait_async_handles(comp_reqs)
                     comp_reqs = []
@@ -424,7 +449,8 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             send_v = _carve(send_bufs[t % 2], 0, (B, Hq, Sq, D), torch.float32)
             target = send_v if t == 0 else dq_delta
             target.zero_()
-            ops.bwd_block(cq, cdo, cl, cd, kc, vc, sm_scale, target, dk_acc, dv_acc, t > 0, kvl)
+            bias = _build_bias(bias_func, local_bias_args, args_cur, cq, kc)
+            ops.bwd_block(cq, cdo, cl, cd, kc, vc, sm_scale, target, dk_acc, dv_acc, t > 0, kvl, bias=bias)
             wait_async_handles(dq_reqs)
             if t > 0:
                 recv_v = _carve(recv_bufs[(t - 1) % 2], 0, (B, Hq, Sq, D), torch.float32)
@@ -443,7 +469,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
                 wait_async_handles(dq_reqs)
                 dq_reqs = []
             if not last:
-                cur = nxt
+                cur, args_cur = nxt, args_next
         wait_async_handles(dq_reqs)
 
     dk = ops.add_cast(dk_acc, None, dt)
@@ -468,12 +494,15 @@ class LVXAttnFunc(torch.autograd.Function):
         ctx.sm_scale = sm_scale
         ctx.causal = causal
         ctx.kv_valid_len = kv_valid_len
+        ctx.bias = (bias_func, local_bias_args, remote_bias_args)      # as the reference keeps them, test.py:52-54
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, L = ctx.saved_tensors
-        dq, dk, dv = _attn_backward(do, q, k, v, o, L, ctx.causal, ctx.sm_scale, None, "flash",
+        bias_func, local_bias_args, remote_bias_args = ctx.bias
+        dq, dk, dv = _attn_backward(do, q, k, v, o, L, ctx.causal, ctx.sm_scale, None, "flash", bias_func=bias_func,
+                                    local_bias_args=local_bias_args, remote_bias_args=remote_bias_args,
                                     kv_valid_len=ctx.kv_valid_len)
         return dq, dk, dv, None, None, None, None, None, None
 

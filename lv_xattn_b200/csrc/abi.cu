@@ -237,6 +237,56 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
                           accumulate_dkdv, sp, static_cast<cudaStream_t>(stream));
 }
 
+int lvx_fwd_block_bias(const lvx_shape* s, const void* q, const void* k, const void* v, const int32_t* kv_valid_len,
+                       const lvx_bias* bias, float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
+  const char* who = "lvx_fwd_block_bias";
+  int rc = check_shape(s, who);
+  if (rc) return rc;
+  if ((rc = check_arch())) return rc;
+  LVX_REQUIRE_PTR(q, who);
+  LVX_REQUIRE_PTR(workspace, who);
+  if (!bias || !bias->bias) return fail(LVX_ERR_NULL, "%s: bias is NULL (use lvx_fwd_block)", who);
+  if (reinterpret_cast<uintptr_t>(bias->bias) & 3u) return fail(LVX_ERR_ALIGN, "%s: bias is not 4-byte aligned", who);
+  if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "%s: sm_scale must be positive", who);
+  if (s->Skv > 0) {
+    LVX_REQUIRE_PTR(k, who);
+    LVX_REQUIRE_PTR(v, who);
+  }
+  FwdPlan p = plan_fwd(*s);
+  if (workspace_bytes < p.o_part_bytes + p.ml_part_bytes)
+    return fail(LVX_ERR_WORKSPACE, "%s: workspace has %zu bytes, %zu needed", who, workspace_bytes,
+                p.o_part_bytes + p.ml_part_bytes);
+  float* o_part = static_cast<float*>(workspace);
+  float* ml_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + p.o_part_bytes);
+  return launch_fwd_block_simt(*s, p, q, k, v, kv_valid_len, bias, sm_scale, o_part, ml_part,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int lvx_bwd_block_bias(const lvx_shape* s, const void* q, const void* d_o, const float* lse, const float* delta,
+                       const void* k, const void* v, const int32_t* kv_valid_len, const lvx_bias* bias, float sm_scale,
+                       float* dq_acc, void* dk_acc, void* dv_acc, int accumulate_dkdv, void* stream) {
+  const char* who = "lvx_bwd_block_bias";
+  int rc = check_shape(s, who);
+  if (rc) return rc;
+  if ((rc = check_arch())) return rc;
+  LVX_REQUIRE_PTR(q, who);
+  LVX_REQUIRE_PTR(d_o, who);
+  LVX_REQUIRE_PTR(lse, who);
+  LVX_REQUIRE_PTR(delta, who);
+  LVX_REQUIRE_PTR(dq_acc, who);
+  if (!bias || !bias->bias) return fail(LVX_ERR_NULL, "%s: bias is NULL (use lvx_bwd_block)", who);
+  if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "%s: sm_scale must be positive", who);
+  if (accumulate_dkdv < 0 || accumulate_dkdv > 2)
+    return fail(LVX_ERR_SHAPE, "%s: accumulate_dkdv must be 0, 1 or 2 (got %d)", who, accumulate_dkdv);
+  if (s->Skv == 0) return LVX_OK;
+  LVX_REQUIRE_PTR(k, who);
+  LVX_REQUIRE_PTR(v, who);
+  LVX_REQUIRE_PTR(dk_acc, who);
+  LVX_REQUIRE_PTR(dv_acc, who);
+  return launch_bwd_block_simt(*s, q, d_o, lse, delta, k, v, kv_valid_len, bias, sm_scale, dq_acc, dk_acc, dv_acc,
+                               accumulate_dkdv, static_cast<cudaStream_t>(stream));
+}
+
 int lvx_fwd_merge_parts(const lvx_shape* s, const float* o_parts, const float* lse_parts, int count,
                         size_t part_stride_o, size_t part_stride_lse, void* o_out, float* lse_out, void* stream) {
   const char* who = "lvx_fwd_merge_parts";

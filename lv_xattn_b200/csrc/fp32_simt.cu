@@ -1,4 +1,6 @@
-// fp32 inputs: forward and backward flash-attention blocks on the FP32 FMA pipe, exact fp32 arithmetic.
+// The general path: forward and backward flash-attention blocks on the FP32 FMA pipe, exact fp32 arithmetic.
+// It serves (1) fp32 inputs and (2) any input dtype when a dense additive bias is given (the reference's
+// bias_func protocol, lv_xattn/attn.py:386-389: S = scale * q.k + bias, bias [B, 1 or H, Sq, Skv] fp32).
 //
 // Why not tf32 on the tensor cores: for 32-bit operands tcgen05 wants K-major tiles in the 16-byte-unit
 // 128B swizzle and MN-major tiles in the 32-byte-unit swizzle. In the backward block every streamed tile
@@ -11,6 +13,8 @@
 // of scores at rows 4*ty.., columns 4*tx.., and for the 64 x 128 products the rows 4*ty.. and the columns
 // tx + 16*c (c = 0..7), which makes every shared-memory access of a warp conflict-free or a broadcast.
 #include "lvx_internal.h"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <math.h>
 
 namespace lvx {
@@ -21,17 +25,41 @@ constexpr int SM_LDP = 65;          // padded row stride of a [64][64] tile
 constexpr int SM_TILE = SM_T * SM_LD;
 constexpr int SM_PTILE = SM_T * SM_LDP;
 
-// Loads rows [row0, row0+64) of a dense [nrows, 128] fp32 matrix into a padded tile; rows past nrows are zero.
-__device__ __forceinline__ void load_tile(float* dst, const float* src, int row0, int nrows, int tid) {
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+__device__ __forceinline__ void from_f32(float* p, float x) { *p = x; }
+__device__ __forceinline__ void from_f32(__nv_bfloat16* p, float x) { *p = __float2bfloat16_rn(x); }
+__device__ __forceinline__ void from_f32(__half* p, float x) { *p = __float2half_rn(x); }
+
+// Loads rows [row0, row0+64) of a dense [nrows, 128] matrix into a padded fp32 tile; rows past nrows are zero.
+template <typename T>
+__device__ __forceinline__ void load_tile(float* dst, const T* src, int row0, int nrows, int tid) {
   for (int idx = tid; idx < SM_T * 128; idx += 256) {
     const int r = idx >> 7, c = idx & 127;
     const int gr = row0 + r;
-    dst[r * SM_LD + c] = gr < nrows ? src[size_t(gr) * 128 + c] : 0.f;
+    dst[r * SM_LD + c] = gr < nrows ? to_f32(src[size_t(gr) * 128 + c]) : 0.f;
   }
 }
 
+// Dense additive bias on the scores: value for (query block, batch, query head, query row, key) at
+// base[blk*s_blk + b*s_b + h*s_h + i*s_q + j*s_kv] (strides in floats; 0 broadcasts). nullptr = no bias.
+struct BiasView {
+  const float* base;
+  long long s_blk, s_b, s_h, s_q, s_kv;
+  int sq, g;          // query rows per head, query heads per KV head (to unpack a packed row)
+};
+// pointer to the bias row of packed row `r` of query slab `slab` (kv slab `kvs`), or nullptr
+__device__ __forceinline__ const float* bias_row(const BiasView& b, int slab, int kvs, int kv_slabs, int hkv, int r) {
+  if (b.base == nullptr) return nullptr;
+  const int blk = slab / kv_slabs, batch = kvs / hkv, hk = kvs % hkv;
+  const int h = hk * b.g + r / b.sq, i = r % b.sq;
+  return b.base + blk * b.s_blk + batch * b.s_b + h * b.s_h + i * b.s_q;
+}
+
 struct Fp32FwdParams {
-  const float *q, *k, *v;
+  const void *q, *k, *v;
+  BiasView bias;
   const int32_t* kv_valid_len;
   int rows, skv, hkv, kv_slabs, nsplit, tiles_per_split;   // tiles_per_split counts 128-row tiles, as in the 16-bit plan
   float scale_log2;
@@ -39,6 +67,7 @@ struct Fp32FwdParams {
   const int* status;   // device status word: non-zero => return at once
 };
 
+template <typename T>
 __global__ void __launch_bounds__(256)
 fp32_fwd_kernel(const Fp32FwdParams p) {
   if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
@@ -55,9 +84,15 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
   if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
   const int kv_begin = min(valid, split * p.tiles_per_split * 128);
   const int kv_end = min(valid, (split + 1) * p.tiles_per_split * 128);
-  const float* qs = p.q + size_t(slab) * p.rows * 128;
-  const float* ks = p.k + size_t(kvs) * p.skv * 128;
-  const float* vs = p.v + size_t(kvs) * p.skv * 128;
+  const T* qs = static_cast<const T*>(p.q) + size_t(slab) * p.rows * 128;
+  const T* ks = static_cast<const T*>(p.k) + size_t(kvs) * p.skv * 128;
+  const T* vs = static_cast<const T*>(p.v) + size_t(kvs) * p.skv * 128;
+  const float* brow[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = mb * SM_T + ty * 4 + i;
+    brow[i] = row < p.rows ? bias_row(p.bias, slab, kvs, p.kv_slabs, p.hkv, row) : nullptr;
+  }
 
   load_tile(sQ, qs, mb * SM_T, p.rows, tid);
   float m[4], l[4], o[4][8];
@@ -95,8 +130,14 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        s[i][j] = (kv0 + tx * 4 + j < kv_end) ? s[i][j] * p.scale_log2 : -INFINITY;
-        mx = fmaxf(mx, s[i][j]);
+        const int col = kv0 + tx * 4 + j;
+        float sc = -INFINITY;
+        if (col < kv_end) {
+          sc = s[i][j] * p.scale_log2;
+          if (brow[i]) sc = fmaf(brow[i][col * p.bias.s_kv], 1.4426950408889634f, sc);   // scale*q.k + bias, base 2
+        }
+        s[i][j] = sc;
+        mx = fmaxf(mx, sc);
       }
 #pragma unroll
       for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -145,15 +186,19 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
 }
 
 struct Fp32BwdParams {
-  const float *q, *d_o, *lse, *delta, *k, *v;
+  const void *q, *d_o, *k, *v;
+  const float *lse, *delta;
+  BiasView bias;
   const int32_t* kv_valid_len;
   int rows, skv, hkv, nblk, kv_slabs;
   float scale, scale_log2;
-  float *dq_acc, *dk_acc, *dv_acc;
+  float *dq_acc;
+  void *dk_acc, *dv_acc;   // fp32 for accumulate 0/1; the input dtype for accumulate 2
   int accumulate;
   const int* status;   // device status word: non-zero => return at once
 };
 
+template <typename T>
 __global__ void __launch_bounds__(256)
 fp32_bwd_kernel(const Fp32BwdParams p) {
   if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
@@ -170,8 +215,8 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
   int valid = p.skv;
   if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
 
-  load_tile(sK, p.k + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
-  load_tile(sV, p.v + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
+  load_tile(sK, static_cast<const T*>(p.k) + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
+  load_tile(sV, static_cast<const T*>(p.v) + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
   float dk[4][8], dv[4][8];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -183,8 +228,8 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
   for (int it = 0; live && it < tiles_per_block * p.nblk; ++it) {
     const int qslab = slab + (it / tiles_per_block) * p.kv_slabs;
     const int q0 = (it % tiles_per_block) * SM_T;
-    const float* qs = p.q + size_t(qslab) * p.rows * 128;
-    const float* dos = p.d_o + size_t(qslab) * p.rows * 128;
+    const T* qs = static_cast<const T*>(p.q) + size_t(qslab) * p.rows * 128;
+    const T* dos = static_cast<const T*>(p.d_o) + size_t(qslab) * p.rows * 128;
     const float* lses = p.lse + size_t(qslab) * p.rows;
     const float* deltas = p.delta + size_t(qslab) * p.rows;
     float* dqs = p.dq_acc + size_t(qslab) * p.rows * 128;
@@ -226,10 +271,14 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
         if (l2 == -INFINITY) l2 = INFINITY;
         dl = deltas[qrow];
       }
+      const float* br = qrow < p.rows ? bias_row(p.bias, qslab, slab, p.kv_slabs, p.hkv, qrow) : nullptr;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const bool ok = kv0 + tx * 4 + j < valid;
-        const float pv = ok ? exp2f(s[i][j] * p.scale_log2 - l2) : 0.f;
+        const int col = kv0 + tx * 4 + j;
+        const bool ok = col < valid;
+        float sc = s[i][j] * p.scale_log2;
+        if (ok && br) sc = fmaf(br[col * p.bias.s_kv], 1.4426950408889634f, sc);
+        const float pv = ok ? exp2f(sc - l2) : 0.f;
         sP[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv;
         sDS[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv * (dp[i][j] - dl);
       }
@@ -286,24 +335,45 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
     const int row = kv0 + ty * 4 + i;
     if (row >= p.skv) continue;
     if (!live && p.accumulate == 1) continue;
-    float* dkp = p.dk_acc + (size_t(slab) * p.skv + row) * 128;
-    float* dvp = p.dv_acc + (size_t(slab) * p.skv + row) * 128;
+    const size_t off = (size_t(slab) * p.skv + row) * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
       const int d = tx + 16 * c;
       const float a = dk[i][c] * p.scale, b = dv[i][c];
-      dkp[d] = p.accumulate == 1 ? dkp[d] + a : a;     // fp32 is its own final dtype (mode 2 == overwrite)
-      dvp[d] = p.accumulate == 1 ? dvp[d] + b : b;
+      if (p.accumulate == 2) {                          // finished gradients in the input dtype
+        from_f32(static_cast<T*>(p.dk_acc) + off + d, a);
+        from_f32(static_cast<T*>(p.dv_acc) + off + d, b);
+      } else {
+        float* dkp = static_cast<float*>(p.dk_acc) + off;
+        float* dvp = static_cast<float*>(p.dv_acc) + off;
+        dkp[d] = p.accumulate == 1 ? dkp[d] + a : a;
+        dvp[d] = p.accumulate == 1 ? dvp[d] + b : b;
+      }
     }
   }
 }
 
-int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, const void* k, const void* v,
-                          const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, cudaStream_t st) {
+static BiasView make_bias(const lvx_shape& s, const lvx_bias* b) {
+  BiasView v;
+  v.base = b ? b->bias : nullptr;
+  v.s_blk = b ? b->stride_block : 0;
+  v.s_b = b ? b->stride_b : 0;
+  v.s_h = b ? b->stride_h : 0;
+  v.s_q = b ? b->stride_q : 0;
+  v.s_kv = b ? b->stride_kv : 0;
+  v.sq = s.Sq;
+  v.g = s.Hq / s.Hkv;
+  return v;
+}
+
+int launch_fwd_block_simt(const lvx_shape& s, const FwdPlan& pl, const void* q, const void* k, const void* v,
+                          const int32_t* kv_valid_len, const lvx_bias* bias, float sm_scale, float* o_part,
+                          float* ml_part, cudaStream_t st) {
   Fp32FwdParams p;
-  p.q = static_cast<const float*>(q);
-  p.k = static_cast<const float*>(k);
-  p.v = static_cast<const float*>(v);
+  p.q = q;
+  p.k = k;
+  p.v = v;
+  p.bias = make_bias(s, bias);
   p.kv_valid_len = kv_valid_len;
   p.rows = pl.rows;
   p.skv = s.Skv;
@@ -316,25 +386,33 @@ int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, 
   p.ml_part = ml_part;
   p.status = device_status_ptr();
   const int smem = (3 * SM_TILE + SM_PTILE) * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(fp32_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 fwd)");
   dim3 grid((pl.rows + SM_T - 1) / SM_T, q_blocks_of(s) * s.B * s.Hkv, pl.nsplit);
-  fp32_fwd_kernel<<<grid, 256, smem, st>>>(p);
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kern) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(p);
+  };
+  if (s.dtype == LVX_FP32) go(fp32_fwd_kernel<float>);
+  else if (s.dtype == LVX_BF16) go(fp32_fwd_kernel<__nv_bfloat16>);
+  else go(fp32_fwd_kernel<__half>);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(simt fwd)");
   e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e, "fp32_fwd_kernel launch");
+  if (e != cudaSuccess) return cuda_fail(e, "simt fwd kernel launch");
   return LVX_OK;
 }
 
-int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
-                          const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
-                          float* dk_acc, float* dv_acc, int accumulate_dkdv, cudaStream_t st) {
+int launch_bwd_block_simt(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
+                          const void* k, const void* v, const int32_t* kv_valid_len, const lvx_bias* bias,
+                          float sm_scale, float* dq_acc, void* dk_acc, void* dv_acc, int accumulate_dkdv,
+                          cudaStream_t st) {
   Fp32BwdParams p;
-  p.q = static_cast<const float*>(q);
-  p.d_o = static_cast<const float*>(d_o);
+  p.q = q;
+  p.d_o = d_o;
   p.lse = lse;
   p.delta = delta;
-  p.k = static_cast<const float*>(k);
-  p.v = static_cast<const float*>(v);
+  p.k = k;
+  p.v = v;
+  p.bias = make_bias(s, bias);
   p.kv_valid_len = kv_valid_len;
   p.rows = (s.Hq / s.Hkv) * s.Sq;
   p.skv = s.Skv;
@@ -349,13 +427,31 @@ int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, co
   p.accumulate = accumulate_dkdv;
   p.status = device_status_ptr();
   const int smem = (4 * SM_TILE + 2 * SM_PTILE) * sizeof(float);
-  cudaError_t e = cudaFuncSetAttribute(fp32_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(fp32 bwd)");
   dim3 grid((s.Skv + SM_T - 1) / SM_T, s.B * s.Hkv, 1);
-  fp32_bwd_kernel<<<grid, 256, smem, st>>>(p);
+  cudaError_t e = cudaSuccess;
+  auto go = [&](auto kern) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess) kern<<<grid, 256, smem, st>>>(p);
+  };
+  if (s.dtype == LVX_FP32) go(fp32_bwd_kernel<float>);
+  else if (s.dtype == LVX_BF16) go(fp32_bwd_kernel<__nv_bfloat16>);
+  else go(fp32_bwd_kernel<__half>);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(simt bwd)");
   e = cudaGetLastError();
-  if (e != cudaSuccess) return cuda_fail(e, "fp32_bwd_kernel launch");
+  if (e != cudaSuccess) return cuda_fail(e, "simt bwd kernel launch");
   return LVX_OK;
+}
+
+int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& pl, const void* q, const void* k, const void* v,
+                          const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, cudaStream_t st) {
+  return launch_fwd_block_simt(s, pl, q, k, v, kv_valid_len, nullptr, sm_scale, o_part, ml_part, st);
+}
+
+int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
+                          const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
+                          float* dk_acc, float* dv_acc, int accumulate_dkdv, cudaStream_t st) {
+  return launch_bwd_block_simt(s, q, d_o, lse, delta, k, v, kv_valid_len, nullptr, sm_scale, dq_acc, dk_acc, dv_acc,
+                               accumulate_dkdv, st);
 }
 
 }  // namespace lvx

@@ -57,6 +57,14 @@ int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& p, const void* q, c
 int launch_bwd_block_fp32(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
                           const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                           float* dk_acc, float* dv_acc, int accumulate_dkdv, cudaStream_t st);
+// The general (FP32-FMA) block kernels: any input dtype, optional dense additive bias.
+int launch_fwd_block_simt(const lvx_shape& s, const FwdPlan& p, const void* q, const void* k, const void* v,
+                          const int32_t* kv_valid_len, const lvx_bias* bias, float sm_scale, float* o_part,
+                          float* ml_part, cudaStream_t st);
+int launch_bwd_block_simt(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
+                          const void* k, const void* v, const int32_t* kv_valid_len, const lvx_bias* bias,
+                          float sm_scale, float* dq_acc, void* dk_acc, void* dv_acc, int accumulate_dkdv,
+                          cudaStream_t st);
 int launch_fwd_merge_parts(const lvx_shape& s, const float* o_parts, const float* lse_parts, int count,
                            size_t stride_o, size_t stride_lse, void* o_out, float* lse_out, cudaStream_t st);
 int launch_sum_cast(const float* parts, int count, size_t stride, void* out, int out_dtype, size_t n, cudaStream_t st);

@@ -100,8 +100,29 @@ class FwdPartials:
         self.shape, self.ws, self.dims, self.dtype, self.device = shape, ws, dims, dtype, device
 
 
-def fwd_partials(q, k, v, sm_scale, kv_valid_len=None) -> FwdPartials:
-    """Launches the forward block: Q block x local K/V shard -> split-KV partials in the workspace."""
+def _bias_view(bias, q, k):
+    """lvx_bias for an fp32 tensor broadcastable to [B, Hq, Sq, Skv] (size-1 dims broadcast, as after the
+    reference's `.expand(B, H, Lq, Lk)`, lv_xattn/attn.py:389). Returns (struct, tensor kept alive)."""
+    _require_cuda(bias)
+    if bias.dtype != torch.float32:
+        bias = bias.float()
+    if q.dim() != 4:
+        raise ValueError("a dense bias is supported for a single query block only")
+    B, Hq, Sq, _ = q.shape
+    Skv = k.shape[2]
+    if bias.dim() != 4:
+        raise ValueError(f"bias must be 4-D, broadcastable to {(B, Hq, Sq, Skv)}; got {tuple(bias.shape)}")
+    try:
+        e = bias.expand(B, Hq, Sq, Skv)
+    except RuntimeError as err:
+        raise ValueError(f"bias {tuple(bias.shape)} does not broadcast to {(B, Hq, Sq, Skv)}") from err
+    sb, sh, sq_, skv_ = e.stride()
+    return _lib.LvxBias(e.data_ptr(), 0, sb, sh, sq_, skv_), e
+
+
+def fwd_partials(q, k, v, sm_scale, kv_valid_len=None, bias=None) -> FwdPartials:
+    """Launches the forward block: Q block x local K/V shard -> split-KV partials in the workspace.
+    bias: optional dense additive fp32 bias on the scores (S = sm_scale*q.k + bias); runs the general kernels."""
     _require_cuda(q, k, v, kv_valid_len)
     lib = _lib.load()
     q, k, v = _contig(q), _contig(k), _contig(v)
@@ -116,9 +137,15 @@ def fwd_partials(q, k, v, sm_scale, kv_valid_len=None) -> FwdPartials:
             raise ValueError("kv_valid_len must be an int32 tensor with one entry per batch element")
         kv_valid_len = _contig(kv_valid_len)
     with _Timed("fwd"):
-        _lib.check(lib.lvx_fwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
-                                     _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale), _lib.ptr(ws), ws.numel(),
-                                     _lib.stream_ptr()), "lvx_fwd_block")
+        if bias is not None:
+            bv, keep = _bias_view(bias, q, k)
+            _lib.check(lib.lvx_fwd_block_bias(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+                                              _lib.ptr(kv_valid_len), ctypes.byref(bv), ctypes.c_float(sm_scale),
+                                              _lib.ptr(ws), ws.numel(), _lib.stream_ptr()), "lvx_fwd_block_bias")
+        else:
+            _lib.check(lib.lvx_fwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+                                         _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale), _lib.ptr(ws), ws.numel(),
+                                         _lib.stream_ptr()), "lvx_fwd_block")
     _count()
     return FwdPartials(shp, ws, tuple(q.shape), q.dtype, q.device)
 
@@ -142,12 +169,12 @@ def fwd_combine(part: FwdPartials, o_in, lse_in, o_out, lse_out, final: bool) ->
     _count()
 
 
-def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, final=True):
+def fwd_block(q, k, v, sm_scale, kv_valid_len=None, o_in=None, lse_in=None, final=True, bias=None):
     """(O, lse) of the Q block against the local K/V shard, merged into the travelling (o_in, lse_in).
 
     final=True  -> O in q.dtype (the caller's result); final=False -> fp32 travelling form.
     lse is fp32 [B*Hq, Sq]."""
-    part = fwd_partials(q, k, v, sm_scale, kv_valid_len)
+    part = fwd_partials(q, k, v, sm_scale, kv_valid_len, bias)
     Hq, Sq = q.shape[-3], q.shape[-2]
     o_out = torch.empty(q.shape, dtype=q.dtype if final else torch.float32, device=q.device)
     lse_out = torch.empty(q.numel() // (Hq * Sq * q.shape[-1]) * Hq, Sq, dtype=torch.float32, device=q.device)
@@ -170,7 +197,8 @@ def bwd_prep(o, do):
     return delta
 
 
-def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None):
+def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None,
+              bias=None):
     """dq_acc += dS K ; dk_acc, dv_acc (+)= dS^T Q, P^T dO.
 
     accumulate_dkdv: False -> overwrite the fp32 dk_acc/dv_acc; True -> add to them; "final" -> dk_acc/dv_acc
@@ -190,6 +218,17 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
         raise ValueError("accumulator sizes do not match q / k / v")
     if kv_valid_len is not None:
         kv_valid_len = _contig(kv_valid_len)
+    mode = 2 if final else (1 if accumulate_dkdv else 0)
+    if bias is not None:
+        bv, keep = _bias_view(bias, q, k)
+        with _Timed("bwd"):
+            _lib.check(lib.lvx_bwd_block_bias(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse),
+                                              _lib.ptr(delta), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len),
+                                              ctypes.byref(bv), ctypes.c_float(sm_scale), _lib.ptr(dq_acc),
+                                              _lib.ptr(dk_acc), _lib.ptr(dv_acc), mode, _lib.stream_ptr()),
+                       "lvx_bwd_block_bias")
+        _count()
+        return
     with _Timed("bwd"):
         _lib.check(lib.lvx_bwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse), _lib.ptr(delta),
                                      _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale),

@@ -26,7 +26,7 @@ from .async_communication import (
     get_slabs,
     wait_async_handles,
 )
-from .attn import _carve, _check_common
+from .attn import _build_bias, _carve, _check_common
 
 
 def _visiting_valid(kv_valid_len, home: int, skv_local: int, device):
@@ -66,6 +66,10 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
     ck, cv = kv_views(cur)
     ck.copy_(k)
     cv.copy_(v)
+    # with a bias_func the "remote" arguments belong to the K/V shard and travel with it (reference
+    # ring/attn.py:246-258); the local ones belong to the queries
+    args_cur = [a.contiguous() for a in remote_bias_args] if bias_func is not None else []
+    args_bufs = [[torch.empty_like(a) for a in args_cur] for _ in range(2)]
     reqs = []
     o_in = l_in = None
     for t in range(steps):
@@ -75,17 +79,19 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         ck, cv = kv_views(cur)
         if not last:
             nxt = bufs[(t + 1) % 2]
-            reqs = _exchange([cur[:2 * n_kv * es]], [nxt[:2 * n_kv * es]], comm_mode)
+            args_next = args_bufs[t % 2]
+            reqs = _exchange([cur[:2 * n_kv * es], *args_cur], [nxt[:2 * n_kv * es], *args_next], comm_mode)
             if no_overlap:
                 wait_async_handles(reqs)
                 reqs = []
         kvl = _visiting_valid(kv_valid_len, (rank - t) % W, Skv, dev)
-        part = ops.fwd_partials(qc, ck, cv, sm_scale, kvl)
+        bias = _build_bias(bias_func, local_bias_args, args_cur, qc, ck)
+        part = ops.fwd_partials(qc, ck, cv, sm_scale, kvl, bias=bias)
         o_out, l_out = (o, L) if last else acc_views(acc[t % 2])
         ops.fwd_combine(part, o_in, l_in, o_out, l_out, last)
         o_in, l_in = o_out, l_out
         if not last:
-            cur = nxt
+            cur, args_cur = nxt, args_next
     wait_async_handles(reqs)
     return q, k, v, o, L
 
@@ -112,7 +118,9 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         kvl = _visiting_valid(kv_valid_len, rank, Skv, dev)
-        ops.bwd_block(qc, doc, Lc, delta, k.contiguous(), v.contiguous(), sm_scale, dq_acc, dk, dv, "final", kvl)
+        bias = _build_bias(bias_func, local_bias_args, remote_bias_args, qc, k)
+        ops.bwd_block(qc, doc, Lc, delta, k.contiguous(), v.contiguous(), sm_scale, dq_acc, dk, dv, "final", kvl,
+                      bias=bias)
         ops.add_cast(dq_acc, None, dt, out=dq)
         return dq, dk, dv
 
@@ -131,6 +139,8 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
     ck.copy_(k)
     cv.copy_(v)
     kv_reqs, g_reqs = [], []
+    args_cur = [a.contiguous() for a in remote_bias_args] if bias_func is not None else []
+    args_bufs = [[torch.empty_like(a) for a in args_cur] for _ in range(2)]
     for t in range(W):
         last = t == W - 1
         wait_async_handles(kv_reqs)
@@ -138,7 +148,8 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         ck, cv = kv_views(cur)
         if not last:
             nxt = kv_bufs[(t + 1) % 2]
-            kv_reqs = _exchange([cur[:2 * n_kv * es]], [nxt[:2 * n_kv * es]], comm_mode)
+            args_next = args_bufs[t % 2]
+            kv_reqs = _exchange([cur[:2 * n_kv * es], *args_cur], [nxt[:2 * n_kv * es], *args_next], comm_mode)
             if no_overlap:
                 wait_async_handles(kv_reqs)
                 kv_reqs = []
@@ -148,14 +159,15 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
         g_reqs = []
         gk, gv = g_views(g_bufs[t % 2])
         kvl = _visiting_valid(kv_valid_len, (rank - t) % W, Skv, dev)
-        ops.bwd_block(qc, doc, Lc, delta, ck, cv, sm_scale, dq_acc, gk, gv, t > 0, kvl)
+        bias = _build_bias(bias_func, local_bias_args, args_cur, qc, ck)
+        ops.bwd_block(qc, doc, Lc, delta, ck, cv, sm_scale, dq_acc, gk, gv, t > 0, kvl, bias=bias)
         # on to rank+1 (after the last step this is the hop that brings every finished accumulator home)
         g_reqs = _exchange([g_bufs[t % 2][:2 * n_kv * 4]], [g_bufs[(t + 1) % 2][:2 * n_kv * 4]], comm_mode)
         if no_overlap:
             wait_async_handles(g_reqs)
             g_reqs = []
         if not last:
-            cur = nxt
+            cur, args_cur = nxt, args_next
     wait_async_handles(g_reqs)
     gk, gv = g_views(g_bufs[W % 2])
     dk = ops.add_cast(gk, None, dt)
@@ -176,11 +188,14 @@ class RingAttnFunc(torch.autograd.Function):
                                       kv_valid_len=kv_valid_len)
         ctx.save_for_backward(q, k, v, o, L)
         ctx.sm_scale, ctx.causal, ctx.kv_valid_len = sm_scale, causal, kv_valid_len
+        ctx.bias = (bias_func, local_bias_args, remote_bias_args)
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, L = ctx.saved_tensors
-        dq, dk, dv = _attn_backward(do, q, k, v, o, L, ctx.causal, ctx.sm_scale, None, "flash",
+        bias_func, local_bias_args, remote_bias_args = ctx.bias
+        dq, dk, dv = _attn_backward(do, q, k, v, o, L, ctx.causal, ctx.sm_scale, None, "flash", bias_func=bias_func,
+                                    local_bias_args=local_bias_args, remote_bias_args=remote_bias_args,
                                     kv_valid_len=ctx.kv_valid_len)
         return dq, dk, dv, None, None, None, None, None, None

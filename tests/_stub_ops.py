@@ -10,8 +10,11 @@ class _Part:
         self.o, self.lse, self.dtype = o, lse, dtype
 
 
-def fwd_partials(q, k, v, sm_scale, kv_valid_len=None):
+def fwd_partials(q, k, v, sm_scale, kv_valid_len=None, bias=None):
     kvl = None if kv_valid_len is None else [int(x) for x in kv_valid_len]
+    if bias is not None:
+        o, lse = orc.attention_fwd(q, k, v, sm_scale, kvl, bias=bias)
+        return _Part(o, lse.reshape(-1, q.shape[2]), q.dtype)
     if q.dim() == 5:      # [n, B, Hq, Sq, D]: every block against the same K/V
         outs = [orc.attention_fwd(qb, k, v, sm_scale, kvl) for qb in q]
         o = torch.stack([a for a, _ in outs])
@@ -38,7 +41,7 @@ def bwd_prep(o, do):
     return (o.float() * do.float()).sum(-1).reshape(-1, S)
 
 
-def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None):
+def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None, bias=None):
     if q.dim() == 5:      # n query blocks, one K/V pass: dK/dV sum over the blocks
         n = q.shape[0]
         rows = lse.numel() // n
@@ -60,6 +63,8 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
     qf, dof = q.float(), do.float()
     ke, ve = orc.expand_kv(k.float(), Hq), orc.expand_kv(v.float(), Hq)
     s = torch.matmul(qf, ke.transpose(2, 3)) * sm_scale
+    if bias is not None:
+        s = s + bias.float()
     if kv_valid_len is not None:
         idx = torch.arange(Skv)[None, None, None, :]
         s = s.masked_fill(idx >= kv_valid_len.view(B, 1, 1, 1).long(), float("-inf"))

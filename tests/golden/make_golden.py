@@ -9,8 +9,10 @@ is present; the fixtures it writes are committed and are what tests/test_oracle.
     python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 2
     python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 4 --seed 2 --heads 1 \
         --sq-per-rank 32 --skv-per-rank 512 --tag _skv2048_seed2
+    python tests/golden/make_golden.py --ref /path/to/LV-XAttn --world 2 --seed 3 --heads 1 --bias --tag _bias
 
-Three shims touch no reference file: the process group is created with gloo before
+Shims that touch no reference file (with --bias a fourth: the bias tensor reports is_cuda, which the reference's
+backward asserts): the process group is created with gloo before
 `lv_xattn.initialize_distributed()` (which then skips its NCCL init, async_communication.py:39-45),
 `torch.cuda.synchronize` is a no-op, and the backward autotuner is pinned to its first config so that it
 does not try to time kernels on a GPU.
@@ -23,7 +25,7 @@ import sys
 import numpy as np
 
 
-def worker(rank, world, ref, port, out_dir, seed=1, heads=2, sq_per_rank=32, skv_per_rank=128, tag=""):
+def worker(rank, world, ref, port, out_dir, seed=1, heads=2, sq_per_rank=32, skv_per_rank=128, tag="", bias=False):
     os.environ.update(TRITON_INTERPRET="1", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                       WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
     sys.dont_write_bytecode = True
@@ -51,9 +53,27 @@ def worker(rank, world, ref, port, out_dir, seed=1, heads=2, sq_per_rank=32, skv
         return x[:, :, rank * n:(rank + 1) * n].contiguous()
 
     ql, dol, kl, vl = sl(q, Sq // world), sl(do, Sq // world), sl(k, Skv // world), sl(v, Skv // world)
-    _, _, _, o, L = lv_xattn._attn_forward(ql, kl, vl, False, scale, None)
+    bias_kw, bias_full = {}, None
+    if bias:
+        # the reference benchmark's bias protocol (test.py:273-286): bias_func(shape, val) puts `val` on the odd key
+        # columns; the shape belongs to the K/V side (local), val travels with the query block (remote). Here val
+        # is 1 + home rank of the query block, so that a block that is merged with the wrong bias shows.
+        class _ReportsCuda(torch.Tensor):        # the reference's backward asserts bias.is_cuda (flash_attn_kernels.py:948)
+            is_cuda = property(lambda self: True)
+
+        def bias_func(shape, val):
+            b = torch.zeros([int(x) for x in shape])
+            b[:, :, :, 1::2] = val
+            return b.as_subclass(_ReportsCuda)
+        bias_kw = dict(bias_func=bias_func,
+                       local_bias_args=[torch.tensor([B, H, Sq // world, Skv // world])],
+                       remote_bias_args=[torch.tensor(float(1 + rank))])
+        bias_full = torch.zeros(B, 1, Sq, Skv)
+        for r in range(world):
+            bias_full[:, :, r * (Sq // world):(r + 1) * (Sq // world), 1::2] = float(1 + r)
+    _, _, _, o, L = lv_xattn._attn_forward(ql, kl, vl, False, scale, None, **bias_kw)
     o, L = o.clone(), L.clone()
-    dq, dk, dv = lv_xattn._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash")
+    dq, dk, dv = lv_xattn._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", **bias_kw)
     outs = {"o": o, "L": L, "dq": dq, "dk": dk, "dv": dv}
     gathered = {}
     for name, t in outs.items():
@@ -64,7 +84,9 @@ def worker(rank, world, ref, port, out_dir, seed=1, heads=2, sq_per_rank=32, skv
     if rank == 0:
         np.savez_compressed(os.path.join(out_dir, f"ref_lvxattn_w{world}{tag}.npz"),
                             q=q.numpy(), k=k.numpy(), v=v.numpy(), do=do.numpy(), scale=np.float32(scale),
-                            world=np.int32(world), **{f"ref_{n}": a.astype(np.float16 if n != "L" else np.float32)
+                            world=np.int32(world),
+                            **({"bias": bias_full.numpy()} if bias_full is not None else {}),
+                            **{f"ref_{n}": a.astype(np.float16 if n != "L" else np.float32)
                                                       for n, a in gathered.items()})
         print("wrote", f"ref_lvxattn_w{world}{tag}.npz")
     dist.destroy_process_group()
@@ -80,8 +102,9 @@ if __name__ == "__main__":
     ap.add_argument("--sq-per-rank", type=int, default=32)
     ap.add_argument("--skv-per-rank", type=int, default=128)
     ap.add_argument("--tag", default="", help="suffix of the fixture's file name")
+    ap.add_argument("--bias", action="store_true", help="run with the reference's bias_func protocol")
     a = ap.parse_args()
     import torch.multiprocessing as mp
     out = os.path.dirname(os.path.abspath(__file__))
-    mp.spawn(worker, args=(a.world, a.ref, a.port, out, a.seed, a.heads, a.sq_per_rank, a.skv_per_rank, a.tag),
+    mp.spawn(worker, args=(a.world, a.ref, a.port, out, a.seed, a.heads, a.sq_per_rank, a.skv_per_rank, a.tag, a.bias),
              nprocs=a.world, join=True)

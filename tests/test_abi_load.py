@@ -46,7 +46,9 @@ def test_python_entry_points_refuse_cpu_tensors():
         lvx._attn_forward(q, q, q, False, 0.1, None)
     with pytest.raises(NotImplementedError):
         lvx._attn_forward(q, q, q, True, 0.1, None)
-    with pytest.raises(NotImplementedError):
-        lvx._attn_forward(q, q, q, False, 0.1, None, bias_func=lambda *a: None)
+    with pytest.raises(ValueError):
+        lvx._attn_forward(q, q, q, False, 0.1, None, bias_func=lambda *a: None)     # bias_func must return a tensor
+    with pytest.raises(ValueError):
+        lvx._attn_forward(q, q, q, False, 0.1, None, local_bias_args=[q])           # arguments without a bias_func
     with pytest.raises(ValueError):
         lvx._attn_forward(q, q[:, :, :, :64], q, False, 0.1, None)

@@ -35,11 +35,29 @@ def _worker(rank, world, port, case, ret):
     ac.initialize_distributed()
     try:
         B, Hq, Hkv, Sq, Skv, dtype, kv_valid, kw = case
+        kw = dict(kw)
         q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 11, dtype)
-        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, SCALE, kv_valid)
+        full_bias = None
+        if kw.pop("bias", False):
+            # the reference's protocol: a KV-side argument stays with the shard, a Q-side argument travels with the
+            # query block, and bias_func builds the step's [B, 1, Sq_l, Skv_l] tile from both (test.py:273-286)
+            gb = torch.Generator().manual_seed(99)
+            key_term = torch.randn(Skv, generator=gb)
+            key_term[1::7] = float("-inf")                      # a mask expressed through the bias
+            qry_term = torch.randn(Sq, generator=gb)
+            full_bias = (qry_term[:, None] + key_term[None, :])[None, None].expand(B, 1, Sq, Skv)
+            n, m = Sq // world, Skv // world
+            kv_side = [key_term[rank * m:(rank + 1) * m].clone()]
+            q_side = [qry_term[rank * n:(rank + 1) * n].clone()]
+            if kw.get("baseline") == "ring":                    # there the travelling arguments belong to the K/V shard
+                kw.update(bias_func=lambda qa, ka: (qa[:, None] + ka[None, :])[None, None].expand(B, 1, -1, -1),
+                          local_bias_args=q_side, remote_bias_args=kv_side)
+            else:
+                kw.update(bias_func=lambda ka, qa: (qa[:, None] + ka[None, :])[None, None].expand(B, 1, -1, -1),
+                          local_bias_args=kv_side, remote_bias_args=q_side)
+        o_ref, lse_ref, dq_ref, dk_ref, dv_ref = orc.attention_fwd_bwd(q, k, v, do, SCALE, kv_valid, bias=full_bias)
         ql, dol = orc.shard(q, rank, world), orc.shard(do, rank, world)
         kl, vl = orc.shard(k, rank, world), orc.shard(v, rank, world)
-        kw = dict(kw)
         mod = attn
         if kw.pop("baseline", None) == "ring":      # the K/V-rotating baseline on the same (stubbed) kernels
             from lv_xattn_b200 import ring
@@ -105,6 +123,17 @@ def test_ring_baseline_fp32(world):
 def test_ring_baseline_bf16_gqa_key_padding():
     _run(4, (2, 4, 1, 32, 256, torch.bfloat16, [200, 40], {"baseline": "ring"}))
     _run(2, (1, 2, 2, 32, 128, torch.float32, None, {"baseline": "ring", "no_overlap": True}))
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_bias_func_protocol(world):
+    """bias_func / local_bias_args / remote_bias_args as in the reference (lv_xattn/attn.py:386-389): the remote
+    arguments travel with the query block, the bias tile of every step is built from both, -inf entries mask."""
+    _run(world, (1, 4, 2, 16 * world, 48 * world, torch.float32, None, {"bias": True}))
+
+
+def test_bias_func_protocol_ring_baseline():
+    _run(2, (1, 2, 2, 32, 96, torch.float32, None, {"bias": True, "baseline": "ring"}))
 
 
 def test_step_loop_no_overlap():

@@ -98,8 +98,13 @@ def test_against_reference_golden_vectors(cuda_device, path):
     zero = torch.zeros_like(k[:, :, :1])
     ke, ve = torch.cat([k, zero], 2).contiguous(), torch.cat([v, zero], 2).contiguous()
     scale = float(g["scale"])
-    _, _, _, o, L = lvx._attn_forward(q, ke, ve, False, scale, None)
-    dq, dk, dv = lvx._attn_backward(do, q, ke, ve, o, L, False, scale, None, "flash")
+    kw = {}
+    if "bias" in g.files:       # fixture made with the reference's bias_func protocol: the general (bias) kernels
+        bias = torch.from_numpy(g["bias"]).to(cuda_device)
+        bias = torch.cat([bias, torch.zeros_like(bias[..., :1])], -1).contiguous()
+        kw = dict(bias_func=lambda b: b, local_bias_args=[bias], remote_bias_args=[])
+    _, _, _, o, L = lvx._attn_forward(q, ke, ve, False, scale, None, **kw)
+    dq, dk, dv = lvx._attn_backward(do, q, ke, ve, o, L, False, scale, None, "flash", **kw)
     B, H, Sq, D = q.shape
     got = {"o": o.float().cpu(), "dq": dq.float().cpu(), "dk": dk[:, :, :-1].float().cpu(), "dv": dv[:, :, :-1].float().cpu()}
     L = L.cpu().view(B, H, Sq)

@@ -3,7 +3,7 @@
 The stated bars are absolute (16-bit: O/dQ/dK/dV max-abs <= 2e-2, lse <= 1e-3; fp32: 1e-4). At long key
 sequences the tensors themselves are far smaller than 2e-2 (softmax averages over many keys), so an absolute
 bar alone cannot fail there. Every comparison therefore also requires, per tensor,
-    ||got - ref||_F / ||ref||_F <= rel_fro        and        max|got - ref| <= rel_max * max|ref|.
+    ||got - ref||_F / ||ref||_F <= rel_fro (1e-2)     and     max|got - ref| <= rel_max * max|ref| (2e-2).
 For bf16 results the floor of the first is the output rounding itself (2^-9 / sqrt(3) ~ 1.1e-3); the bars below
 leave a factor of a few over what the kernels measure, and an all-zero or half-scaled tensor fails them at any size.
 """
@@ -12,8 +12,10 @@ import os
 
 import torch
 
-# name -> (abs, rel_fro, rel_max) for 16-bit inputs
-BF16 = {"o": (2e-2, 1e-2, 5e-2), "dq": (2e-2, 1e-2, 5e-2), "dk": (2e-2, 1e-2, 5e-2), "dv": (2e-2, 1e-2, 5e-2)}
+# name -> (abs, rel_fro, rel_max) for 16-bit inputs. Measured over the whole GPU suite on a B200: relative Frobenius
+# error at most 2.9e-3 (O 2.6e-3, dQ 2.9e-3, dK 2.9e-3, dV 2.4e-3), max error / max|ref| at most 5.3e-3; the bars are
+# about 3x that.
+BF16 = {"o": (2e-2, 1e-2, 2e-2), "dq": (2e-2, 1e-2, 2e-2), "dk": (2e-2, 1e-2, 2e-2), "dv": (2e-2, 1e-2, 2e-2)}
 LSE_ABS_16 = 1e-3
 FP32_ABS = 1e-4
 FP32_REL_FRO = 1e-4
@@ -33,7 +35,7 @@ def errors(got: torch.Tensor, ref: torch.Tensor):
     return max_abs, rel_fro, rel_max
 
 
-def assert_close(got, ref, name, label="", abs_tol=2e-2, rel_fro=1e-2, rel_max=5e-2):
+def assert_close(got, ref, name, label="", abs_tol=2e-2, rel_fro=1e-2, rel_max=2e-2):
     """got vs ref under the three criteria; `name` is o/dq/dk/dv, `label` identifies the case in the message."""
     assert got.shape == ref.shape, f"{label} {name}: shape {tuple(got.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(got.float()).all(), f"{label} {name}: non-finite values"

@@ -142,6 +142,23 @@ int lvx_bwd_block_bias(const lvx_shape* s, const void* q, const void* d_o, const
                        const void* k, const void* v, const int32_t* kv_valid_len, const lvx_bias* bias,
                        float sm_scale, float* dq_acc, void* dk_acc, void* dv_acc, int accumulate_dkdv, void* stream);
 
+/* K/V projection of the visual states with the per-head RMSNorm of K fused in: one tensor-core GEMM
+ *   Kpre = X Wk^T, V = X Wv^T,   K = Kpre * rsqrt(mean_d(Kpre^2) + eps) * norm_w   (per key and head, d = 0..127)
+ * X [batch, S, Kd], Wk/Wv [Hkv*128, Kd] (row-major, the nn.Linear layout), norm_w [128]; all in `dtype` (LVX_BF16
+ * or LVX_FP16). Outputs are written in the layout the attention kernels read: K, V [batch, Hkv, S, 128] in `dtype`,
+ * and rstd [batch, Hkv, S] fp32 (nullable) for the backward of the norm. norm_w NULL = no norm. Kd must be a
+ * multiple of 64 and Hkv even. Replaces k_proj / v_proj + view/transpose + repeat_kv + k_norm of the reference's
+ * patched layer, test_llama3.py:394-419, which run in forward and again in the backward recompute (:197, :235). */
+int lvx_kv_project(int dtype, const void* x, const void* wk, const void* wv, const void* norm_w, float eps,
+                   int batch, int S, int Kd, int Hkv, void* k_out, void* v_out, float* rstd, void* stream);
+
+/* Backward of that norm: dKpre = rstd * (norm_w * dK - (K / norm_w) * mean_d(K * dK)) and
+ * dw[d] += sum over rows of dK * K / norm_w (dw fp32 [128], zeroed by the caller). K, dK, dKpre: `rows` rows of
+ * 128 in `dtype` ([batch, Hkv, S, 128] flattened), rstd fp32 [rows]. The reference lets autograd do this through
+ * MllamaTextRMSNorm (test_llama3.py:419). */
+int lvx_knorm_bwd(int dtype, const void* k, const void* dk, const float* rstd, const void* norm_w, void* dkpre,
+                  float* dw, size_t rows, void* stream);
+
 /* Merge of `count` finished partial results of the same query block, each computed against a different
  * K/V shard: o_parts fp32 [count][B*Hq*Sq*D], lse_parts fp32 [count][B*Hq*Sq] -> o_out (shape.dtype) and
  * lse_out, with the same stable log-sum-exp merge as lvx_fwd_combine_merge ((0,-inf) is the neutral

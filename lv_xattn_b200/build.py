@@ -14,7 +14,7 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(PKG_DIR, "liblvx.so")
-SOURCES = ["abi.cu", "selftest.cu", "fwd_sm100.cu", "elementwise.cu", "bwd_sm100.cu", "noalloc.cu", "fp32_simt.cu", "p2p.cu"]
+SOURCES = ["abi.cu", "selftest.cu", "fwd_sm100.cu", "elementwise.cu", "bwd_sm100.cu", "noalloc.cu", "fp32_simt.cu", "p2p.cu", "kvproj_sm100.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr",

@@ -287,6 +287,43 @@ int lvx_bwd_block_bias(const lvx_shape* s, const void* q, const void* d_o, const
                                accumulate_dkdv, static_cast<cudaStream_t>(stream));
 }
 
+int lvx_kv_project(int dtype, const void* x, const void* wk, const void* wv, const void* norm_w, float eps, int batch,
+                   int S, int Kd, int Hkv, void* k_out, void* v_out, float* rstd, void* stream) {
+  const char* who = "lvx_kv_project";
+  int rc = check_arch();
+  if (rc) return rc;
+  if (dtype != LVX_BF16 && dtype != LVX_FP16) return fail(LVX_ERR_DTYPE, "%s: dtype %d unsupported (bf16 or fp16)", who, dtype);
+  if (batch <= 0 || S <= 0 || Kd <= 0 || Hkv <= 0) return fail(LVX_ERR_SHAPE, "%s: non-positive dimension", who);
+  if (Kd % 64) return fail(LVX_ERR_SHAPE, "%s: Kd=%d is not a multiple of 64", who, Kd);
+  if (Hkv % 2) return fail(LVX_ERR_SHAPE, "%s: Hkv=%d is odd (tiles hold two heads)", who, Hkv);
+  if (int64_t(batch) * S > (int64_t(1) << 31) - 512) return fail(LVX_ERR_SHAPE, "%s: batch*S too large", who);
+  if (!(eps >= 0.f)) return fail(LVX_ERR_SHAPE, "%s: eps must be non-negative", who);
+  LVX_REQUIRE_PTR(x, who);
+  LVX_REQUIRE_PTR(wk, who);
+  LVX_REQUIRE_PTR(wv, who);
+  LVX_REQUIRE_PTR(k_out, who);
+  LVX_REQUIRE_PTR(v_out, who);
+  if (norm_w && (reinterpret_cast<uintptr_t>(norm_w) & 1u)) return fail(LVX_ERR_ALIGN, "%s: norm_w is misaligned", who);
+  int* sp = status_ptr();
+  if (!sp) return fail(LVX_ERR_DRIVER, "%s: status word unavailable", who);
+  return launch_kv_project(dtype, x, wk, wv, norm_w, eps, batch, S, Kd, Hkv, k_out, v_out, rstd, sp,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int lvx_knorm_bwd(int dtype, const void* k, const void* dk, const float* rstd, const void* norm_w, void* dkpre,
+                  float* dw, size_t rows, void* stream) {
+  const char* who = "lvx_knorm_bwd";
+  if (dtype != LVX_BF16 && dtype != LVX_FP16) return fail(LVX_ERR_DTYPE, "%s: dtype %d unsupported (bf16 or fp16)", who, dtype);
+  if (rows == 0) return LVX_OK;
+  LVX_REQUIRE_PTR(k, who);
+  LVX_REQUIRE_PTR(dk, who);
+  LVX_REQUIRE_PTR(rstd, who);
+  LVX_REQUIRE_PTR(dkpre, who);
+  LVX_REQUIRE_PTR(dw, who);
+  if (!norm_w || (reinterpret_cast<uintptr_t>(norm_w) & 7u)) return fail(LVX_ERR_ALIGN, "%s: norm_w must be given, 8-byte aligned", who);
+  return launch_knorm_bwd(dtype, k, dk, rstd, norm_w, dkpre, dw, long(rows), static_cast<cudaStream_t>(stream));
+}
+
 int lvx_fwd_merge_parts(const lvx_shape* s, const float* o_parts, const float* lse_parts, int count,
                         size_t part_stride_o, size_t part_stride_lse, void* o_out, float* lse_out, void* stream) {
   const char* who = "lvx_fwd_merge_parts";

@@ -65,6 +65,12 @@ int launch_bwd_block_simt(const lvx_shape& s, const void* q, const void* d_o, co
                           const void* k, const void* v, const int32_t* kv_valid_len, const lvx_bias* bias,
                           float sm_scale, float* dq_acc, void* dk_acc, void* dv_acc, int accumulate_dkdv,
                           cudaStream_t st);
+// K/V projection with fused per-head RMSNorm (kvproj_sm100.cu) and the backward of that norm.
+int launch_kv_project(int dtype, const void* x, const void* wk, const void* wv, const void* norm_w, float eps,
+                      int batch, int s, int kd, int hkv, void* k_out, void* v_out, float* rstd, int* status,
+                      cudaStream_t st);
+int launch_knorm_bwd(int dtype, const void* k, const void* dk, const float* rstd, const void* norm_w, void* dkpre,
+                     float* dw, long rows, cudaStream_t st);
 int launch_fwd_merge_parts(const lvx_shape& s, const float* o_parts, const float* lse_parts, int count,
                            size_t stride_o, size_t stride_lse, void* o_out, float* lse_out, cudaStream_t st);
 int launch_sum_cast(const float* parts, int count, size_t stride, void* out, int out_dtype, size_t n, cudaStream_t st);

@@ -26,6 +26,7 @@ import torch.distributed as dist
 
 from .async_communication import get_sequence_parallel_group, get_sequence_parallel_rank, get_sequence_parallel_size
 from .attn import LVXAttnRecomputeFunc, RingAttnRecomputeFunc
+from .projection import kv_project
 
 ATTENTION_MODES = ("lv_xattn", "ring", "ring_self")      # the reference's modes (test_llama3.py:107)
 
@@ -79,10 +80,20 @@ def patch_cross_attention_forward(attention_mode="lv_xattn"):
         def project(x, states):
             q = self.q_proj(x).view(bsz, q_len, nh, hd).transpose(1, 2)
             q = self.q_norm(q)
-            k = self.k_proj(states).view(bsz, -1, nkv, hd).transpose(1, 2)
-            v = self.v_proj(states).view(bsz, -1, nkv, hd).transpose(1, 2)
-            k = self.k_norm(k)
-            return q.contiguous(), k.contiguous(), v.contiguous()
+            # K/V of the visual states: one fused GEMM with the norm in its epilogue, written in the kernels' layout
+            # (projection.KVProjectFunc); the module path is kept for tensors it does not take (CPU, fp32, biases)
+            fused = None
+            if hd == 128 and self.k_proj.bias is None and self.v_proj.bias is None:
+                eps = getattr(self.k_norm, "variance_epsilon", getattr(self.k_norm, "eps", 1e-6))
+                fused = kv_project(states, self.k_proj.weight, self.v_proj.weight, self.k_norm.weight, eps, nkv)
+            if fused is not None:
+                k, v = fused
+            else:
+                k = self.k_proj(states).view(bsz, -1, nkv, hd).transpose(1, 2)
+                v = self.v_proj(states).view(bsz, -1, nkv, hd).transpose(1, 2)
+                k = self.k_norm(k).contiguous()
+                v = v.contiguous()
+            return q.contiguous(), k, v
 
         params = [p for p in (self.q_proj.weight, self.k_proj.weight, self.v_proj.weight, self.q_norm.weight,
                               self.k_norm.weight)]

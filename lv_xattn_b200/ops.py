@@ -13,12 +13,12 @@ _workspaces: dict = {}
 # Launch accounting for benchmarks: number of kernels of this library launched since the last reset, and
 # (when profiling is on) CUDA event pairs around the two tensor-core kernels, recorded on the launch stream.
 launch_count = 0
-_profile = None   # None, or {"fwd": [(start, end), ...], "bwd": [...]}
+_profile = None   # None, or {"fwd": [(start, end), ...], "bwd": [...], "proj": [...]}
 
 
 def set_profiling(on: bool) -> None:
     global _profile
-    _profile = {"fwd": [], "bwd": []} if on else None
+    _profile = {"fwd": [], "bwd": [], "proj": []} if on else None
 
 
 def take_profile():
@@ -27,7 +27,7 @@ def take_profile():
     global _profile
     out = {k: [a.elapsed_time(b) for a, b in v] for k, v in (_profile or {}).items()}
     if _profile is not None:
-        _profile = {"fwd": [], "bwd": []}
+        _profile = {"fwd": [], "bwd": [], "proj": []}
     return out
 
 
@@ -236,6 +236,56 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
                                      2 if final else (1 if accumulate_dkdv else 0), None, 0,
                                      _lib.stream_ptr()), "lvx_bwd_block")
     _count()
+
+
+def kv_project_supported(states, wk, wv, n_kv_heads: int) -> bool:
+    """True when lvx_kv_project can take these tensors (CUDA, bf16/fp16, head dim 128, Kd a multiple of 64, an even
+    number of KV heads, plain [out, in] weights)."""
+    return (states.is_cuda and states.dtype in (torch.bfloat16, torch.float16) and states.dim() == 3
+            and wk.dtype == states.dtype and wv.dtype == states.dtype and wk.shape == wv.shape
+            and wk.shape == (n_kv_heads * 128, states.shape[-1]) and states.shape[-1] % 64 == 0
+            and n_kv_heads % 2 == 0)
+
+
+def kv_project(states, wk, wv, norm_weight, eps: float, n_kv_heads: int):
+    """K = rmsnorm_per_head(states @ wk^T) * norm_weight, V = states @ wv^T in one tensor-core GEMM, written as
+    [B, Hkv, S, 128]; also rstd [B, Hkv, S] fp32. norm_weight None = no norm."""
+    _require_cuda(states, wk, wv, norm_weight)
+    lib = _lib.load()
+    if not kv_project_supported(states, wk, wv, n_kv_heads):
+        raise ValueError("kv_project: unsupported shapes or dtypes (see kv_project_supported)")
+    states, wk, wv = _contig(states), _contig(wk), _contig(wv)
+    B, S, Kd = states.shape
+    if norm_weight is not None:
+        if norm_weight.numel() != 128:
+            raise ValueError("norm_weight must have 128 entries")
+        norm_weight = _contig(norm_weight.to(states.dtype))
+    k = torch.empty(B, n_kv_heads, S, 128, dtype=states.dtype, device=states.device)
+    v = torch.empty_like(k)
+    rstd = torch.empty(B, n_kv_heads, S, dtype=torch.float32, device=states.device)
+    with _Timed("proj"):
+        _lib.check(lib.lvx_kv_project(_lib.dtype_code(states.dtype), _lib.ptr(states), _lib.ptr(wk), _lib.ptr(wv),
+                                      _lib.ptr(norm_weight), ctypes.c_float(eps), B, S, Kd, n_kv_heads, _lib.ptr(k),
+                                      _lib.ptr(v), _lib.ptr(rstd), _lib.stream_ptr()), "lvx_kv_project")
+    _count()
+    return k, v, rstd
+
+
+def knorm_bwd(k, dk, rstd, norm_weight):
+    """Backward of the fused K norm: (dKpre like k, dw fp32 [128])."""
+    _require_cuda(k, dk, rstd, norm_weight)
+    lib = _lib.load()
+    k, dk, rstd = _contig(k), _contig(dk), _contig(rstd)
+    if dk.dtype != k.dtype or dk.shape != k.shape or rstd.dtype != torch.float32 or rstd.numel() * 128 != k.numel():
+        raise ValueError("knorm_bwd: k, dk [.., 128] in one 16-bit dtype and fp32 rstd with one entry per row")
+    w = _contig(norm_weight.to(k.dtype))
+    dkpre = torch.empty_like(k)
+    dw = torch.zeros(128, dtype=torch.float32, device=k.device)
+    _lib.check(lib.lvx_knorm_bwd(_lib.dtype_code(k.dtype), _lib.ptr(k), _lib.ptr(dk), _lib.ptr(rstd), _lib.ptr(w),
+                                 _lib.ptr(dkpre), _lib.ptr(dw), ctypes.c_size_t(rstd.numel()), _lib.stream_ptr()),
+               "lvx_knorm_bwd")
+    _count()
+    return dkpre, dw
 
 
 def fwd_merge_parts(o_parts, lse_parts, out_dtype, o_out=None, lse_out=None):

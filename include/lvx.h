@@ -259,7 +259,30 @@ typedef struct lvx_push_segment {
                        * world*src_stride bytes from it */
 } lvx_push_segment;
 int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
-                 uint32_t epoch, void* stream);
+                 uint32_t epoch, int skip_self, void* stream);
+/* skip_self != 0: the segments are stored into the peers' buffers only (this rank's own copy is filled by the
+ * caller, e.g. with a local copy that need not wait for the link); the epoch is still published to every rank. */
+
+/* Fused exchange + compute: lvx_fwd_block / lvx_bwd_block on a gathered buffer ([q_blocks, B, Hq, Sq, D] etc.)
+ * whose blocks are still being stored by the other ranks (lvx_p2p_push on their side) while the kernel runs. The
+ * kernel starts with block `first_block` (this rank's own, in place at launch) and walks the others in ring order;
+ * before it first touches block b it waits -- bounded by lvx_p2p_set_timeout, 0x1300 | b in the status word on
+ * time-out -- until word [slot][b] of this rank's flag array has reached `epoch`. The transfer of the remote blocks
+ * thus overlaps the work on the local one instead of preceding the launch. my_flags NULL: no waits, block order only.
+ * This is the reference's "post the transfer for the next block, compute on the current one" overlap
+ * (lv_xattn/attn.py:369-377, :481-498) moved inside one kernel launch. bf16 / fp16 only. */
+typedef struct lvx_block_wait {
+  const uint32_t* my_flags;   /* this rank's flag array (device pointer), LVX_P2P_SLOTS x LVX_MAX_PEERS words */
+  int32_t slot;
+  uint32_t epoch;
+  int32_t first_block;        /* 0 .. q_blocks-1 */
+} lvx_block_wait;
+int lvx_fwd_block_gathered(const lvx_shape* s, const void* q, const void* k, const void* v,
+                           const int32_t* kv_valid_len, float sm_scale, void* workspace, size_t workspace_bytes,
+                           const lvx_block_wait* wait, void* stream);
+int lvx_bwd_block_gathered(const lvx_shape* s, const void* q, const void* d_o, const float* lse, const float* delta,
+                           const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
+                           float* dk_acc, float* dv_acc, int accumulate_dkdv, const lvx_block_wait* wait, void* stream);
 int lvx_p2p_wait(const uint32_t* my_flags, int world, int slot, uint32_t epoch, void* stream);
 
 /* Self-test of the tensor-core building blocks (TMA tile load, shared-memory and TMEM operand

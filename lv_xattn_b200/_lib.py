@@ -20,7 +20,7 @@ _DTYPE = {torch.bfloat16: LVX_BF16, torch.float16: LVX_FP16, torch.float32: LVX_
 SYMBOLS = [
     "lvx_version", "lvx_last_error", "lvx_device_status", "lvx_device_status_peek", "lvx_p2p_set_timeout",
     "lvx_query_workspace", "lvx_fwd_block", "lvx_fwd_block_bias", "lvx_bwd_block_bias",
-    "lvx_kv_project", "lvx_knorm_bwd",
+    "lvx_kv_project", "lvx_knorm_bwd", "lvx_fwd_block_gathered", "lvx_bwd_block_gathered",
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
     "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
     "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast", "lvx_p2p_push", "lvx_p2p_wait",
@@ -41,6 +41,11 @@ class LvxPeers(ctypes.Structure):
 class LvxBias(ctypes.Structure):
     _fields_ = [("bias", ctypes.c_void_p)] + [(n, ctypes.c_int64) for n in
                                                ("stride_block", "stride_b", "stride_h", "stride_q", "stride_kv")]
+
+
+class LvxBlockWait(ctypes.Structure):
+    _fields_ = [("my_flags", ctypes.c_void_p), ("slot", ctypes.c_int32), ("epoch", ctypes.c_uint32),
+                ("first_block", ctypes.c_int32)]
 
 
 class LvxPushSegment(ctypes.Structure):
@@ -77,6 +82,10 @@ def load():
     bp = ctypes.POINTER(LvxBias)
     lib.lvx_fwd_block_bias.argtypes = [sp, vp, vp, vp, i32p, bp, ctypes.c_float, vp, ctypes.c_size_t, vp]
     lib.lvx_bwd_block_bias.argtypes = [sp, vp, vp, fp, fp, vp, vp, i32p, bp, ctypes.c_float, fp, vp, vp, ctypes.c_int, vp]
+    wp = ctypes.POINTER(LvxBlockWait)
+    lib.lvx_fwd_block_gathered.argtypes = [sp, vp, vp, vp, i32p, ctypes.c_float, vp, ctypes.c_size_t, wp, vp]
+    lib.lvx_bwd_block_gathered.argtypes = [sp, vp, vp, fp, fp, vp, vp, i32p, ctypes.c_float, fp, fp, fp, ctypes.c_int,
+                                           wp, vp]
     lib.lvx_kv_project.argtypes = [ctypes.c_int, vp, vp, vp, vp, ctypes.c_float, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                    ctypes.c_int, vp, vp, fp, vp]
     lib.lvx_knorm_bwd.argtypes = [ctypes.c_int, vp, vp, fp, vp, vp, fp, ctypes.c_size_t, vp]

@@ -48,7 +48,7 @@ _SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
 
 
 _DEFAULT_SCHEDULE = "auto"
-_AUTO_PEER_SCHEDULE = "p2p_pull"     # the peer-memory form "auto" picks
+_AUTO_PEER_SCHEDULE = os.environ.get("LVX_AUTO_PEER_SCHEDULE", "p2p")     # the peer-memory form "auto" picks
 
 
 def _schedule(schedule, like=None):
@@ -162,15 +162,28 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
     if sched == "p2p":
         from . import peer_memory as pm
         pm.status_watch.poll()
+        rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
-        # every rank stores its Q block into all ranks' gathered buffer (posted NVLink stores) and signals
+        main, side = torch.cuda.current_stream(dev), pm.side_stream(dev)
+        # Fused exchange + compute. The Q block goes into this rank's own slot of the gathered buffer with a local
+        # copy and to the peers' slots from a side stream (posted NVLink stores + epoch); the multi-block kernel
+        # starts at once with the local block and waits, inside the kernel and block by block, for the others.
         e = pm.next_epoch(pm.SLOT_FWD_Q)
         qbuf = pm.get_peer_buffer("p2p_q_all", 2 * W * n_o * es, dev)
         q_off = (e & 1) * W * n_o * es
-        ops.p2p_push(qbuf.peers, flag_peers, [(qc, False, q_off, n_o * es)], pm.SLOT_FWD_Q, e)
-        ops.p2p_wait(my_flags, W, pm.SLOT_FWD_Q, e)
         q_all = _carve(qbuf.local, q_off, (W, B, Hq, Sq, D), dt)
-        part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl)
+        q_all[rank].copy_(qc)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ready)              # after everything the caller queued, and after the previous exchange
+            ops.p2p_push(qbuf.peers, flag_peers, [(qc, False, q_off, n_o * es)], pm.SLOT_FWD_Q, e, skip_self=True)
+            pushed = torch.cuda.Event()
+            pushed.record(side)
+        wait = (my_flags, pm.SLOT_FWD_Q, e, rank) if dt != torch.float32 else None
+        if wait is None:
+            ops.p2p_wait(my_flags, W, pm.SLOT_FWD_Q, e)
+        part = ops.fwd_partials(q_all, kc, vc, sm_scale, kvl, block_wait=wait)
         sbuf = get_slabs("g_acc_send", W * (n_o + n_l) * 4, dev, 1)[0]
         o_parts = _carve(sbuf, 0, (W, B, Hq, Sq, D), torch.float32)
         l_parts = _carve(sbuf, W * n_o * 4, (W * B * Hq, Sq), torch.float32)
@@ -186,6 +199,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         o_recv = _carve(pbuf.local, p_off, (W, B, Hq, Sq, D), torch.float32)
         l_recv = _carve(pbuf.local, p_off + W * n_o * 4, (W, B * Hq, Sq), torch.float32)
         ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
+        main.wait_event(pushed)                 # the caller may reuse q once this call's kernels are done
         pm.status_watch.post()
         return q, k, v, o, L
     if sched == "p2p_pull":
@@ -329,31 +343,47 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
     if sched == "p2p":
         from . import peer_memory as pm
         pm.status_watch.poll()
+        rank = pm.get_sequence_parallel_rank()
         flag_peers, my_flags = pm.get_flags(dev)
+        main, side = torch.cuda.current_stream(dev), pm.side_stream(dev)
         e = pm.next_epoch(pm.SLOT_BWD_IN)
         blk = W * (2 * n_q * es + 2 * n_r * 4)
         ibuf = pm.get_peer_buffer("p2p_bwd_all", 2 * blk, dev)
         base = (e & 1) * blk
         offs = (base, base + W * n_q * es, base + 2 * W * n_q * es, base + 2 * W * n_q * es + W * n_r * 4)
-        ops.p2p_push(ibuf.peers, flag_peers, [(qc, False, offs[0], n_q * es), (doc, False, offs[1], n_q * es),
-                                              (Lc, False, offs[2], n_r * 4), (delta, False, offs[3], n_r * 4)],
-                     pm.SLOT_BWD_IN, e)
-        ops.p2p_wait(my_flags, W, pm.SLOT_BWD_IN, e)
         q_all = _carve(ibuf.local, offs[0], (W, B, Hq, Sq, D), dt)
         do_all = _carve(ibuf.local, offs[1], (W, B, Hq, Sq, D), dt)
         l_all = _carve(ibuf.local, offs[2], (W * B * Hq, Sq), torch.float32)
         d_all = _carve(ibuf.local, offs[3], (W * B * Hq, Sq), torch.float32)
+        # own block with local copies; the peers' slots from the side stream while the kernel already works
+        q_all[rank].copy_(qc)
+        do_all[rank].copy_(doc)
+        l_all.view(W, B * Hq, Sq)[rank].copy_(Lc)
+        d_all.view(W, B * Hq, Sq)[rank].copy_(delta)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ready)
+            ops.p2p_push(ibuf.peers, flag_peers, [(qc, False, offs[0], n_q * es), (doc, False, offs[1], n_q * es),
+                                                  (Lc, False, offs[2], n_r * 4), (delta, False, offs[3], n_r * 4)],
+                         pm.SLOT_BWD_IN, e, skip_self=True)
+            pushed = torch.cuda.Event()
+            pushed.record(side)
         dq_parts = _carve(get_slabs("g_dq_send", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
         dq_parts.zero_()
         dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
-        ops.bwd_block(q_all, do_all, l_all, d_all, kc, vc, sm_scale, dq_parts, dk, dv, "final", kvl)
+        wait = (my_flags, pm.SLOT_BWD_IN, e, rank) if dt != torch.float32 else None
+        if wait is None:
+            ops.p2p_wait(my_flags, W, pm.SLOT_BWD_IN, e)
+        ops.bwd_block(q_all, do_all, l_all, d_all, kc, vc, sm_scale, dq_parts, dk, dv, "final", kvl, block_wait=wait)
         e = pm.next_epoch(pm.SLOT_BWD_DQ)
         dbuf = pm.get_peer_buffer("p2p_dq_recv", 2 * W * n_q * 4, dev)
         d_off = (e & 1) * W * n_q * 4
         ops.p2p_push(dbuf.peers, flag_peers, [(dq_parts, True, d_off, n_q * 4)], pm.SLOT_BWD_DQ, e)
         ops.p2p_wait(my_flags, W, pm.SLOT_BWD_DQ, e)
         ops.sum_cast(_carve(dbuf.local, d_off, (W, B, Hq, Sq, D), torch.float32), dt, out=dq)
+        main.wait_event(pushed)
         _end_of_backward_status(pm)
         return dq, dk, dv
     elif sched == "p2p_pull":

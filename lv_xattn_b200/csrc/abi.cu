@@ -160,10 +160,30 @@ int lvx_query_workspace(const lvx_shape* s, size_t* fwd_bytes, size_t* bwd_bytes
   return LVX_OK;
 }
 
+static int check_block_wait(const lvx_shape* s, const lvx_block_wait* w, const char* who) {
+  if (!w) return LVX_OK;
+  if (s->dtype == LVX_FP32) return fail(LVX_ERR_DTYPE, "%s: the fp32 kernels do not take a block wait", who);
+  const int qb = s->q_blocks > 1 ? s->q_blocks : 1;
+  if (w->first_block < 0 || w->first_block >= qb) return fail(LVX_ERR_SHAPE, "%s: first_block %d outside [0, %d)", who, w->first_block, qb);
+  if (w->my_flags) {
+    if (w->slot < 0 || w->slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, w->slot);
+    if (qb > LVX_MAX_PEERS) return fail(LVX_ERR_SHAPE, "%s: %d blocks but only %d flag words per slot", who, qb, LVX_MAX_PEERS);
+    if (reinterpret_cast<uintptr_t>(w->my_flags) & 3u) return fail(LVX_ERR_ALIGN, "%s: my_flags is misaligned", who);
+  }
+  return LVX_OK;
+}
+
 int lvx_fwd_block(const lvx_shape* s, const void* q, const void* k, const void* v, const int32_t* kv_valid_len,
                   float sm_scale, void* workspace, size_t workspace_bytes, void* stream) {
-  const char* who = "lvx_fwd_block";
+  return lvx_fwd_block_gathered(s, q, k, v, kv_valid_len, sm_scale, workspace, workspace_bytes, nullptr, stream);
+}
+
+int lvx_fwd_block_gathered(const lvx_shape* s, const void* q, const void* k, const void* v, const int32_t* kv_valid_len,
+                           float sm_scale, void* workspace, size_t workspace_bytes, const lvx_block_wait* wait,
+                           void* stream) {
+  const char* who = wait ? "lvx_fwd_block_gathered" : "lvx_fwd_block";
   int rc = check_shape(s, who);
+  if (!rc) rc = check_block_wait(s, wait, who);
   if (rc) return rc;
   if ((rc = check_arch())) return rc;
   LVX_REQUIRE_PTR(q, who);
@@ -181,7 +201,7 @@ int lvx_fwd_block(const lvx_shape* s, const void* q, const void* k, const void* 
   float* o_part = static_cast<float*>(workspace);
   float* ml_part = reinterpret_cast<float*>(static_cast<char*>(workspace) + p.o_part_bytes);
   return launch_fwd_block(*s, p, q, k, v, kv_valid_len, sm_scale, o_part, ml_part, sp,
-                          static_cast<cudaStream_t>(stream));
+                          static_cast<cudaStream_t>(stream), wait);
 }
 
 int lvx_fwd_combine_merge(const lvx_shape* s, const void* workspace, const float* o_in, const float* lse_in,
@@ -215,10 +235,18 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
                   const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
                   float* dk_acc, float* dv_acc, int accumulate_dkdv, void* workspace, size_t workspace_bytes,
                   void* stream) {
-  const char* who = "lvx_bwd_block";
   (void)workspace;
   (void)workspace_bytes;
+  return lvx_bwd_block_gathered(s, q, d_o, lse, delta, k, v, kv_valid_len, sm_scale, dq_acc, dk_acc, dv_acc,
+                                accumulate_dkdv, nullptr, stream);
+}
+
+int lvx_bwd_block_gathered(const lvx_shape* s, const void* q, const void* d_o, const float* lse, const float* delta,
+                           const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
+                           float* dk_acc, float* dv_acc, int accumulate_dkdv, const lvx_block_wait* wait, void* stream) {
+  const char* who = wait ? "lvx_bwd_block_gathered" : "lvx_bwd_block";
   int rc = check_shape(s, who);
+  if (!rc) rc = check_block_wait(s, wait, who);
   if (rc) return rc;
   if ((rc = check_arch())) return rc;
   LVX_REQUIRE_PTR(q, who);
@@ -234,7 +262,7 @@ int lvx_bwd_block(const lvx_shape* s, const void* q, const void* d_o, const floa
   int* sp = status_ptr();
   if (!sp) return fail(LVX_ERR_DRIVER, "%s: status word unavailable", who);
   return launch_bwd_block(*s, q, d_o, lse, delta, k, v, kv_valid_len, sm_scale, dq_acc, dk_acc, dv_acc,
-                          accumulate_dkdv, sp, static_cast<cudaStream_t>(stream));
+                          accumulate_dkdv, sp, static_cast<cudaStream_t>(stream), wait);
 }
 
 int lvx_fwd_block_bias(const lvx_shape* s, const void* q, const void* k, const void* v, const int32_t* kv_valid_len,

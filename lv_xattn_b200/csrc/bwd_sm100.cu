@@ -38,6 +38,7 @@
 //   warp  25    tcgen05.mma issuer; owns the TMEM allocation
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
+#include "block_wait.cuh"
 #include <cuda_fp16.h>
 #include <math.h>
 #include <stdio.h>
@@ -97,6 +98,7 @@ struct BwdParams {
   float* dk_acc;       // [slab][skv][128]  (fp32; 16-bit when accumulate == 2)
   float* dv_acc;
   int accumulate;      // 0 overwrite fp32, 1 add to fp32, 2 write the finished gradient in the input dtype
+  BlockWait bw;        // query blocks that may still be arriving from other ranks
   int* status;
 };
 
@@ -186,11 +188,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tX = tmem_base + TM_X + lane_sel, tY = tmem_base + TM_Y + lane_sel;
       const float c = p.scale_log2;
-      // tile j -> (query slab, first row inside the block)
-      auto tile_slab = [&](int j) { return slab + (j / nq) * p.kv_slabs; };
+      // tile j -> (query slab, first row inside the block); blocks are walked starting with this rank's own
+      auto tile_slab = [&](int j) { return slab + ((p.bw.first_blk + j / nq) % p.nblk) * p.kv_slabs; };
       auto tile_row0 = [&](int j) { return (j % nq) * 128; };
       // Per-column statistics of a query tile: threads 0-127 fetch lse, 128-255 delta (warps 0-7).
       auto fetch_stat = [&](int j) -> float {
+        // the first tile of a block that another rank sends: its statistics must have landed
+        if (tid < 256 && (j % nq) == 0 && !wait_block(p.bw, (p.bw.first_blk + j / nq) % p.nblk, abort_flag, p.status))
+          return 0.f;
         const int qrow = tile_row0(j) + (tid & 127);
         const size_t stat_base = size_t(tile_slab(j)) * p.rows;
         if (tid < 128) {
@@ -369,7 +374,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         {
           const int row0 = (j % nq) * 128 + ch * 64;
           const int ncols = min(64, p.rows - row0);
-          float* dst = p.dq_acc + (size_t(slab + (j / nq) * p.kv_slabs) * p.rows + row0) * 128 + d;
+          float* dst = p.dq_acc + (size_t(slab + ((p.bw.first_blk + j / nq) % p.nblk) * p.kv_slabs) * p.rows + row0) * 128 + d;
 #pragma unroll
           for (int i = 0; i < 64; ++i)
             if (i < ncols) atomicAdd(dst + size_t(i) * 128, __uint_as_float(v[i >> 5][i & 31]) * p.scale);
@@ -392,7 +397,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         for (int j = 0; j < ntot; ++j) {
           const int s = j % BWD_NSQ;
           const uint32_t ph = (j / BWD_NSQ) & 1;
-          const int qslab = slab + (j / nq) * p.kv_slabs, y = (j % nq) * 128;
+          const int blk = (p.bw.first_blk + j / nq) % p.nblk;
+          const int qslab = slab + blk * p.kv_slabs, y = (j % nq) * 128;
+          if (y == 0) {      // first tile of a block: it may still be on its way from another rank
+            if (!wait_block(p.bw, blk, abort_flag, p.status)) break;
+            fence_async_global();
+          }
           if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY))) break;
           uint8_t* dstq = smem + BWD_OFF_Q + s * 2 * BWD_TILE;
           mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_TILE);
@@ -540,7 +550,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
                      const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
-                     float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st) {
+                     float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st,
+                     const lvx_block_wait* bw) {
   if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "lvx_bwd_block: sm_scale must be positive");
   if (accumulate_dkdv < 0 || accumulate_dkdv > 2)
     return fail(LVX_ERR_SHAPE, "lvx_bwd_block: accumulate_dkdv must be 0, 1 or 2 (got %d)", accumulate_dkdv);
@@ -576,6 +587,7 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   p.dv_acc = dv_acc;
   p.accumulate = accumulate_dkdv;
   p.status = status;
+  p.bw = make_block_wait(bw, qb);
 
   dim3 grid((s.Skv + 127) / 128, s.B * s.Hkv, 1);
   cudaError_t e = cudaSuccess;

@@ -77,17 +77,27 @@ fwd_combine_kernel(const float* __restrict__ o_part, const float* __restrict__ m
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float lsum = 0.f;
   if (mmax != -INFINITY) {
-    for (int s = 0; s < nsplit; ++s) {
-      const size_t prow = (size_t(slab) * nsplit + s) * rows_per_slab + r;
-      const float2 ml = *reinterpret_cast<const float2*>(ml_part + prow * 2);
-      if (ml.x == -INFINITY) continue;
-      const float w = exp2f(ml.x - mmax);
-      lsum += ml.y * w;
-      const float4 v = reinterpret_cast<const float4*>(o_part + prow * 128)[lane];
-      acc.x += v.x * w;
-      acc.y += v.y * w;
-      acc.z += v.z * w;
-      acc.w += v.w * w;
+    // four splits per round: the statistics and the partial rows of all four are requested before any is used
+    for (int s0 = 0; s0 < nsplit; s0 += 4) {
+      float2 ml[4];
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int s = min(s0 + u, nsplit - 1);
+        const size_t prow = (size_t(slab) * nsplit + s) * rows_per_slab + r;
+        ml[u] = *reinterpret_cast<const float2*>(ml_part + prow * 2);
+        v[u] = reinterpret_cast<const float4*>(o_part + prow * 128)[lane];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (s0 + u >= nsplit || ml[u].x == -INFINITY) continue;
+        const float w = exp2f(ml[u].x - mmax);
+        lsum += ml[u].y * w;
+        acc.x += v[u].x * w;
+        acc.y += v[u].y * w;
+        acc.z += v[u].z * w;
+        acc.w += v[u].w * w;
+      }
     }
   }
   // (O_loc, lse_loc) of this shard

@@ -18,6 +18,7 @@
 //   Q tiles so that the tensor core works on one tile while the other is in its softmax.
 #include "lvx_internal.h"
 #include "sm100_prims.cuh"
+#include "block_wait.cuh"
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -58,6 +59,7 @@ struct FwdParams {
   float scale_log2;     // sm_scale * log2(e)
   float* o_part;        // [B*Hkv][nsplit][rows][128]
   float* ml_part;       // [B*Hkv][nsplit][rows][2]
+  BlockWait bw;         // query blocks that may still be arriving from other ranks
   int* status;
 };
 
@@ -87,8 +89,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mb = blockIdx.x, bh = blockIdx.y, split = blockIdx.z;
-  const int kvs = bh % p.kv_slabs;      // K/V slab of this query slab
+  const int mb = blockIdx.x, split = blockIdx.z;
+  const int kvs = blockIdx.y % p.kv_slabs;      // K/V slab of this query slab
+  // query blocks are scheduled starting with this rank's own (which is in place at launch)
+  const int nblk = gridDim.y / p.kv_slabs;
+  const int blk = (p.bw.first_blk + int(blockIdx.y) / p.kv_slabs) % nblk;
+  const int bh = blk * p.kv_slabs + kvs;        // query slab
   const int batch = kvs / p.hkv;
 
   // K/V tile range of this CTA, clipped to the valid prefix of the shard.
@@ -298,13 +304,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         tma_prefetch_desc(&tmQ);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
-        mbar_arrive_expect_tx(&bars[FB_Q_FULL], 2 * FWD_TILE_BYTES);
-        for (int t = 0; t < 2; ++t)
-          for (int h = 0; h < 2; ++h)
-            tma_load_3d(smem + FWD_OFF_Q + t * FWD_TILE_BYTES + h * FWD_HALF_BYTES, &tmQ, &bars[FB_Q_FULL], h * 64,
-                        mb * 256 + t * 128, bh);
+        const bool q_here = wait_block(p.bw, blk, abort_flag, p.status);
+        if (q_here) {
+          fence_async_global();
+          mbar_arrive_expect_tx(&bars[FB_Q_FULL], 2 * FWD_TILE_BYTES);
+          for (int t = 0; t < 2; ++t)
+            for (int h = 0; h < 2; ++h)
+              tma_load_3d(smem + FWD_OFF_Q + t * FWD_TILE_BYTES + h * FWD_HALF_BYTES, &tmQ, &bars[FB_Q_FULL], h * 64,
+                          mb * 256 + t * 128, bh);
+        }
         int k_issued = 0, v_issued = 0;
-        for (int j = 0; j < n; ++j) {
+        for (int j = 0; q_here && j < n; ++j) {
           const int s = j % FWD_NS;
           const uint32_t ph = (j / FWD_NS) & 1;
           const int y = (tile0 + j) * 128;
@@ -325,7 +335,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const long long t0 = clock64();
             while (!mbar_try_wait(bar, ph) && clock64() - t0 < LVX_SPIN_LIMIT_CYCLES) {}
           };
-          drain(&bars[FB_Q_FULL], 0);
+          if (q_here) drain(&bars[FB_Q_FULL], 0);
           for (int j = max(0, k_issued - FWD_NS); j < k_issued; ++j) drain(&bars[FB_K_FULL + j % FWD_NS], (j / FWD_NS) & 1);
           for (int j = max(0, v_issued - FWD_NS); j < v_issued; ++j) drain(&bars[FB_V_FULL + j % FWD_NS], (j / FWD_NS) & 1);
         }
@@ -491,7 +501,7 @@ FwdPlan plan_fwd(const lvx_shape& s) {
 
 int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const void* k, const void* v,
                      const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, int* status,
-                     cudaStream_t st) {
+                     cudaStream_t st, const lvx_block_wait* bw) {
   if (!(sm_scale > 0.f)) return fail(LVX_ERR_SHAPE, "lvx_fwd_block: sm_scale must be positive");
   if (s.dtype == LVX_FP32) return launch_fwd_block_fp32(s, pl, q, k, v, kv_valid_len, sm_scale, o_part, ml_part, st);
   (void)num_sms;
@@ -524,6 +534,7 @@ int launch_fwd_block(const lvx_shape& s, const FwdPlan& pl, const void* q, const
   p.o_part = o_part;
   p.ml_part = ml_part;
   p.status = status;
+  p.bw = make_block_wait(bw, qb);
 
   dim3 grid(pl.m_blocks, qb * s.B * s.Hkv, pl.nsplit);
   cudaError_t e = cudaSuccess;

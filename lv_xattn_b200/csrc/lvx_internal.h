@@ -43,14 +43,17 @@ FwdPlan plan_fwd(const lvx_shape& s);
 // Launchers (one per .cu). `status` is the device status word.
 int launch_fwd_block(const lvx_shape& s, const FwdPlan& p, const void* q, const void* k, const void* v,
                      const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, int* status,
-                     cudaStream_t st);
+                     cudaStream_t st, const lvx_block_wait* bw = nullptr);
 int launch_fwd_combine(const lvx_shape& s, const FwdPlan& p, const float* o_part, const float* ml_part,
                        const float* o_in, const float* lse_in, void* o_out, float* lse_out, int out_is_final,
                        cudaStream_t st);
 int launch_bwd_prep(const lvx_shape& s, const void* o, const void* d_o, float* delta, cudaStream_t st);
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
                      const void* k, const void* v, const int32_t* kv_valid_len, float sm_scale, float* dq_acc,
-                     float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st);
+                     float* dk_acc, float* dv_acc, int accumulate_dkdv, int* status, cudaStream_t st,
+                     const lvx_block_wait* bw = nullptr);
+// Limit of the in-kernel waits for a peer's flag, in SM cycles (lvx_p2p_set_timeout).
+long long p2p_wait_limit_cycles();
 // fp32 inputs (exact FP32-FMA kernels, same workspace layout and masking rules as the tensor-core path)
 int launch_fwd_block_fp32(const lvx_shape& s, const FwdPlan& p, const void* q, const void* k, const void* v,
                           const int32_t* kv_valid_len, float sm_scale, float* o_part, float* ml_part, cudaStream_t st);

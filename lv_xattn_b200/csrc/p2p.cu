@@ -31,6 +31,8 @@ namespace lvx {
 // stall, an evaluation on one rank), so the wait for its flag has its own limit, set at run time in seconds
 // (lvx_p2p_set_timeout; 120 s unless changed) and converted to SM cycles with the device's peak clock.
 static double g_wait_seconds = 120.0;
+static long long wait_limit_cycles();
+long long p2p_wait_limit_cycles() { return wait_limit_cycles(); }
 static long long wait_limit_cycles() {
   static int khz[64] = {};
   int dev = 0;
@@ -103,11 +105,24 @@ p2p_gather_kernel(PeerPtrs src, size_t src_offset, size_t bytes, uint8_t* __rest
   const size_t n16 = bytes >> 4;
   const size_t total = n16 * world;
   const size_t gstride = size_t(gridDim.x) * blockDim.x;
-  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += gstride) {
-    const int s = int(i / n16);
-    const size_t off = (i - size_t(s) * n16) << 4;
-    const float4 v = ld_cg_f4(src.p[s] + src_offset + off);
-    *reinterpret_cast<float4*>(dst + size_t(s) * dst_stride + off) = v;
+  // loads over NVLink are round trips: four in flight per thread
+  for (size_t i0 = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * gstride) {
+    float4 v[4];
+    uint8_t* d[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const size_t i = i0 + size_t(u) * gstride;
+      d[u] = nullptr;
+      if (i < total) {
+        const int s = int(i / n16);
+        const size_t off = (i - size_t(s) * n16) << 4;
+        v[u] = ld_cg_f4(src.p[s] + src_offset + off);
+        d[u] = dst + size_t(s) * dst_stride + off;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (d[u]) *reinterpret_cast<float4*>(d[u]) = v[u];
   }
 }
 
@@ -197,6 +212,7 @@ struct PushSeg {
 struct PushArgs {
   PushSeg seg[LVX_P2P_MAX_SEGMENTS];
   int nseg;
+  int skip_self;     // 1: this rank's own copy of the buffer is filled by the caller, only the peers are written
 };
 
 __device__ unsigned int g_push_done[LVX_P2P_SLOTS];
@@ -211,12 +227,26 @@ p2p_push_kernel(PeerPtrs dst, PeerPtrs flags, PushArgs a, int world, int rank, i
     const PushSeg sg = a.seg[g];
     const size_t n16 = sg.bytes >> 4;
     const size_t total = n16 * world;
-    for (size_t i = gtid; i < total; i += gstride) {
-      const int s = int(i / n16);
-      const size_t off = (i - size_t(s) * n16) << 4;
-      const float4 v = *reinterpret_cast<const float4*>(sg.src + size_t(s) * sg.src_stride + off);
-      uint8_t* d = const_cast<uint8_t*>(dst.p[s]) + sg.dst_offset + size_t(rank) * sg.dst_rank_stride + off;
-      *reinterpret_cast<float4*>(d) = v;
+    // four 16-byte chunks per thread and round, all loads issued before the first (posted) store, so that the
+    // copy is bound by the link and not by one load-store round trip at a time
+    for (size_t i0 = gtid; i0 < total; i0 += 4 * gstride) {
+      float4 v[4];
+      uint8_t* d[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const size_t i = i0 + size_t(u) * gstride;
+        d[u] = nullptr;
+        if (i < total) {
+          const int r = int(i / n16);
+          if (a.skip_self && r == rank) continue;
+          const size_t off = (i - size_t(r) * n16) << 4;
+          v[u] = *reinterpret_cast<const float4*>(sg.src + size_t(r) * sg.src_stride + off);
+          d[u] = const_cast<uint8_t*>(dst.p[r]) + sg.dst_offset + size_t(rank) * sg.dst_rank_stride + off;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (d[u]) *reinterpret_cast<float4*>(d[u]) = v[u];
     }
   }
   __threadfence_system();
@@ -361,7 +391,7 @@ int lvx_p2p_sum_cast(const lvx_peers* parts, size_t offset, void* out, int out_d
 }
 
 int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
-                 uint32_t epoch, void* stream) {
+                 uint32_t epoch, int skip_self, void* stream) {
   const char* who = "lvx_p2p_push";
   int rc = peers_ok(dst, who);
   if (rc) return rc;
@@ -372,6 +402,7 @@ int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_se
   if ((rc = range_ok(flags, 0, sizeof(uint32_t) * LVX_P2P_SLOTS * LVX_MAX_PEERS, who, "the flag array"))) return rc;
   PushArgs a;
   a.nseg = nseg;
+  a.skip_self = skip_self ? 1 : 0;
   size_t most = 0;
   for (int g = 0; g < nseg; ++g) {
     const lvx_push_segment& u = segments[g];

@@ -72,6 +72,39 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // ---------------------------------------------------------------------------------------------
+// Query blocks that arrive from other GPUs while the kernel runs
+// ---------------------------------------------------------------------------------------------
+// A multi-block launch may start before the blocks of the other ranks have landed in this GPU's gathered buffer:
+// the peers store them (plain stores over NVLink) and then release-store an epoch number into this GPU's flag word
+// of the block. Whoever is about to read block `blk` first waits here, at most `limit` cycles. The local block
+// (first_blk) is in place before the launch and never waits. flags == nullptr: everything is in place.
+struct BlockWait {
+  const uint32_t* flags;     // this GPU's flag words of the slot, one per rank
+  uint32_t epoch;
+  int first_blk;             // block processed first (this rank's own)
+  long long limit;           // cycles
+};
+// Returns false when the block did not arrive in time (the status word then holds 0x1300 | blk).
+__device__ __forceinline__ bool wait_block(const BlockWait& w, int blk, volatile int* abort_flag, int* status) {
+  if (w.flags == nullptr || blk == w.first_blk) return true;
+  const uint32_t* f = w.flags + blk;
+  const long long t0 = clock64();
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (static_cast<int32_t>(v - w.epoch) >= 0) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > w.limit) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, LVX_DEV_TIMEOUT_BASE | 0x300 | blk);
+      return false;
+    }
+  }
+}
+// Orders what this thread has observed (the peer's data, after wait_block) before its following TMA loads.
+__device__ __forceinline__ void fence_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
 // TMA
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {

@@ -120,7 +120,13 @@ def _bias_view(bias, q, k):
     return _lib.LvxBias(e.data_ptr(), 0, sb, sh, sq_, skv_), e
 
 
-def fwd_partials(q, k, v, sm_scale, kv_valid_len=None, bias=None) -> FwdPartials:
+def _block_wait(block_wait):
+    """(my_flags tensor or None, slot, epoch, first_block) -> LvxBlockWait (see lvx_fwd_block_gathered)."""
+    flags, slot, epoch, first = block_wait
+    return _lib.LvxBlockWait(None if flags is None else flags.data_ptr(), slot, epoch & 0xFFFFFFFF, first)
+
+
+def fwd_partials(q, k, v, sm_scale, kv_valid_len=None, bias=None, block_wait=None) -> FwdPartials:
     """Launches the forward block: Q block x local K/V shard -> split-KV partials in the workspace.
     bias: optional dense additive fp32 bias on the scores (S = sm_scale*q.k + bias); runs the general kernels."""
     _require_cuda(q, k, v, kv_valid_len)
@@ -142,6 +148,12 @@ def fwd_partials(q, k, v, sm_scale, kv_valid_len=None, bias=None) -> FwdPartials
             _lib.check(lib.lvx_fwd_block_bias(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
                                               _lib.ptr(kv_valid_len), ctypes.byref(bv), ctypes.c_float(sm_scale),
                                               _lib.ptr(ws), ws.numel(), _lib.stream_ptr()), "lvx_fwd_block_bias")
+        elif block_wait is not None:
+            bw = _block_wait(block_wait)
+            _lib.check(lib.lvx_fwd_block_gathered(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
+                                                  _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale), _lib.ptr(ws),
+                                                  ws.numel(), ctypes.byref(bw), _lib.stream_ptr()),
+                       "lvx_fwd_block_gathered")
         else:
             _lib.check(lib.lvx_fwd_block(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v),
                                          _lib.ptr(kv_valid_len), ctypes.c_float(sm_scale), _lib.ptr(ws), ws.numel(),
@@ -198,7 +210,7 @@ def bwd_prep(o, do):
 
 
 def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumulate_dkdv, kv_valid_len=None,
-              bias=None):
+              bias=None, block_wait=None):
     """dq_acc += dS K ; dk_acc, dv_acc (+)= dS^T Q, P^T dO.
 
     accumulate_dkdv: False -> overwrite the fp32 dk_acc/dv_acc; True -> add to them; "final" -> dk_acc/dv_acc
@@ -227,6 +239,16 @@ def bwd_block(q, do, lse, delta, k, v, sm_scale, dq_acc, dk_acc, dv_acc, accumul
                                               ctypes.byref(bv), ctypes.c_float(sm_scale), _lib.ptr(dq_acc),
                                               _lib.ptr(dk_acc), _lib.ptr(dv_acc), mode, _lib.stream_ptr()),
                        "lvx_bwd_block_bias")
+        _count()
+        return
+    if block_wait is not None:
+        bw = _block_wait(block_wait)
+        with _Timed("bwd"):
+            _lib.check(lib.lvx_bwd_block_gathered(ctypes.byref(shp), _lib.ptr(q), _lib.ptr(do), _lib.ptr(lse),
+                                                  _lib.ptr(delta), _lib.ptr(k), _lib.ptr(v), _lib.ptr(kv_valid_len),
+                                                  ctypes.c_float(sm_scale), _lib.ptr(dq_acc), _lib.ptr(dk_acc),
+                                                  _lib.ptr(dv_acc), mode, ctypes.byref(bw), _lib.stream_ptr()),
+                       "lvx_bwd_block_gathered")
         _count()
         return
     with _Timed("bwd"):
@@ -371,10 +393,11 @@ def p2p_sum_cast(parts_peers, offset: int, out, my_flags, slot: int, epoch: int)
     _count()
 
 
-def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int):
+def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int, skip_self: bool = False):
     """One launch: for every rank s and every segment (src tensor, all_to_all, dst_offset, dst_rank_stride),
     copies src (all_to_all False: the whole tensor to everyone; True: its block s, src being [W, ...]) into rank
-    s's buffer at dst_offset + rank*dst_rank_stride, then publishes `epoch` for `slot` to every rank."""
+    s's buffer at dst_offset + rank*dst_rank_stride, then publishes `epoch` for `slot` to every rank.
+    skip_self: this rank's own buffer is not written (the caller fills it), the epoch still goes to everyone."""
     lib = _lib.load()
     W = dst_peers.world
     arr = (_lib.LvxPushSegment * len(segments))()
@@ -392,7 +415,8 @@ def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int):
         arr[i].bytes = nbytes
         arr[i].src_bytes = total
     _lib.check(lib.lvx_p2p_push(ctypes.byref(dst_peers), ctypes.byref(flags_peers), arr, len(segments), slot,
-                                ctypes.c_uint32(epoch & 0xFFFFFFFF), _lib.stream_ptr()), "lvx_p2p_push")
+                                ctypes.c_uint32(epoch & 0xFFFFFFFF), 1 if skip_self else 0, _lib.stream_ptr()),
+               "lvx_p2p_push")
     _count()
 
 

@@ -180,6 +180,17 @@ def check_device_status():
     status_watch.check()
 
 
+_SIDE = {}
+
+
+def side_stream(device):
+    """The stream the outgoing stores of the fused schedule run on, one per device."""
+    key = str(device)
+    if key not in _SIDE:
+        _SIDE[key] = torch.cuda.Stream(device)
+    return _SIDE[key]
+
+
 def next_epoch(slot: int) -> int:
     _EPOCHS[slot] += 1
     return _EPOCHS[slot]

@@ -75,3 +75,59 @@ def test_merge_parts_and_sum_cast(cuda_device):
     s = ops.sum_cast(parts, torch.float32)
     assert torch.allclose(s, parts.sum(0), atol=1e-5)
     assert ops.sum_cast(parts, torch.bfloat16).dtype == torch.bfloat16
+
+
+def test_gathered_blocks_with_in_kernel_waits(cuda_device):
+    """lvx_fwd_block_gathered / lvx_bwd_block_gathered: the multi-block launch that starts with its own block and
+    checks a per-block flag before touching the others. Here every flag is already at the epoch (the "peers" stored
+    their blocks earlier in the same stream), so the kernels never wait for a later launch; results must equal the
+    plain multi-block launch bit for bit (dQ: to fp32 reassociation), for every choice of the first block."""
+    import ctypes
+    from lv_xattn_b200 import ops, _lib
+    n, B, Hq, Hkv, Sq, Skv = 4, 1, 8, 2, 128, 1024
+    d = cuda_device
+    _, k, v, _ = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 70, torch.bfloat16)
+    qs = torch.stack([orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 71 + i, torch.bfloat16)[0] for i in range(n)]).to(d)
+    dos = torch.stack([orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 71 + i, torch.bfloat16)[3] for i in range(n)]).to(d)
+    kd, vd = k.to(d), v.to(d)
+    o_ref, lse_ref = ops.fwd_block(qs, kd, vd, SCALE)
+    delta = ops.bwd_prep(o_ref, dos)
+
+    def bwd(block_wait):
+        dq = torch.zeros(qs.shape, dtype=torch.float32, device=d)
+        dk = torch.empty(k.shape, dtype=torch.bfloat16, device=d)
+        dv = torch.empty(k.shape, dtype=torch.bfloat16, device=d)
+        ops.bwd_block(qs, dos, lse_ref, delta, kd, vd, SCALE, dq, dk, dv, "final", block_wait=block_wait)
+        return dq, dk, dv
+
+    dq_ref, dk_ref, dv_ref = bwd(None)
+    flags = torch.zeros(_lib.P2P_SLOTS * _lib.MAX_PEERS, dtype=torch.int32, device=d)
+    flags.view(_lib.P2P_SLOTS, _lib.MAX_PEERS)[3, :n] = 7            # every block has reached epoch 7 on slot 3
+    for first in range(n):
+        for fl in (flags, None):                                      # with flags, and block order only
+            part = ops.fwd_partials(qs, kd, vd, SCALE, block_wait=(fl, 3, 7, first))
+            o = torch.empty_like(o_ref)
+            lse = torch.empty_like(lse_ref)
+            ops.fwd_combine(part, None, None, o, lse, True)
+            assert torch.equal(o, o_ref) and torch.equal(lse, lse_ref)
+            dq, dk, dv = bwd((fl, 3, 7, first))
+            assert (dq - dq_ref).norm().item() <= 2e-5 * dq_ref.norm().item()
+            # dK/dV sum over the blocks in TMEM in walk order: a different first block is a different fp32 order
+            assert (dk.float() - dk_ref.float()).abs().max().item() <= 2e-2 * dk_ref.float().abs().max().item()
+            assert (dv.float() - dv_ref.float()).abs().max().item() <= 2e-2 * dv_ref.float().abs().max().item()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    # a block whose flag nothing sets: with the limit at a millisecond the kernel gives up and says which block
+    lib = _lib.load()
+    try:
+        _lib.check(lib.lvx_p2p_set_timeout(ctypes.c_double(1e-3)), "lvx_p2p_set_timeout")
+        flags.view(_lib.P2P_SLOTS, _lib.MAX_PEERS)[3, 2] = 6          # block 2 is one epoch behind
+        ops.fwd_partials(qs, kd, vd, SCALE, block_wait=(flags, 3, 7, 0))
+        torch.cuda.synchronize()
+        assert _lib.device_status() == (0x1300 | 2)
+        bwd((flags, 3, 7, 1))
+        torch.cuda.synchronize()
+        assert _lib.device_status() == (0x1300 | 2)
+    finally:
+        _lib.check(lib.lvx_p2p_set_timeout(ctypes.c_double(120.0)), "lvx_p2p_set_timeout")
+        _lib.device_status()

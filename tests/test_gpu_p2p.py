@@ -101,6 +101,17 @@ def test_push_all_gather_and_all_to_all(dev, world):
         for r in range(world):
             assert torch.equal(recv[r][par, 0], torch.stack(own))
             assert torch.equal(recv[r][par, 1], torch.stack([parts[c][r] for c in range(world)]))
+    # skip_self: the peers are written, this rank's own buffer is left to the caller, the epoch reaches everyone
+    recv2 = [torch.zeros(world, n, device=dev) for _ in range(world)]
+    own = [torch.randn(n, device=dev) for _ in range(world)]
+    for r in range(world):
+        ops.p2p_push(_peers(recv2, r), _peers(flags, r), [(own[r], False, 0, n * 4)], 6, 1, skip_self=True)
+    for r in range(world):
+        ops.p2p_wait(flags[r], world, 6, 1)
+    torch.cuda.synchronize()
+    for r in range(world):
+        for c in range(world):
+            assert torch.equal(recv2[r][c], own[c] if c != r else torch.zeros(n, device=dev))
     assert _lib.device_status() == 0
 
 

@@ -263,6 +263,13 @@ int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_se
 /* skip_self != 0: the segments are stored into the peers' buffers only (this rank's own copy is filled by the
  * caller, e.g. with a local copy that need not wait for the link); the epoch is still published to every rank. */
 
+/* lvx_p2p_push done by the copy engines instead of a kernel: one cudaMemcpyAsync per peer and segment followed by
+ * a 4-byte copy of the epoch into that peer's flag word, all on `stream` (copies of one stream complete in order, so
+ * a flag never overtakes its data). It needs no SM, so it proceeds while a kernel of this library that fills the
+ * GPU -- and may itself be waiting for peers inside lvx_*_block_gathered -- is running on another stream. */
+int lvx_p2p_push_dma(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
+                     uint32_t epoch, int skip_self, void* stream);
+
 /* Fused exchange + compute: lvx_fwd_block / lvx_bwd_block on a gathered buffer ([q_blocks, B, Hq, Sq, D] etc.)
  * whose blocks are still being stored by the other ranks (lvx_p2p_push on their side) while the kernel runs. The
  * kernel starts with block `first_block` (this rank's own, in place at launch) and walks the others in ring order;

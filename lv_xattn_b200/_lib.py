@@ -24,6 +24,7 @@ SYMBOLS = [
     "lvx_fwd_combine_merge", "lvx_bwd_prep", "lvx_bwd_block", "lvx_add_cast", "lvx_selftest_mma",
     "lvx_fwd_block_static", "lvx_fwd_merge_parts", "lvx_sum_cast",
     "lvx_p2p_signal", "lvx_p2p_gather", "lvx_p2p_fwd_merge", "lvx_p2p_sum_cast", "lvx_p2p_push", "lvx_p2p_wait",
+    "lvx_p2p_push_dma",
 ]
 MAX_PEERS = 16      # LVX_MAX_PEERS
 P2P_SLOTS = 8       # LVX_P2P_SLOTS

@@ -48,6 +48,7 @@ _SUPPORTED = (torch.bfloat16, torch.float16, torch.float32)
 
 
 _DEFAULT_SCHEDULE = "auto"
+_PUSH_DMA = os.environ.get("LVX_PUSH", "dma") == "dma"   # outgoing blocks of the fused schedule: copy engines or a kernel
 _AUTO_PEER_SCHEDULE = os.environ.get("LVX_AUTO_PEER_SCHEDULE", "p2p")     # the peer-memory form "auto" picks
 
 
@@ -177,9 +178,14 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         ready.record(main)
         with torch.cuda.stream(side):
             side.wait_event(ready)              # after everything the caller queued, and after the previous exchange
-            ops.p2p_push(qbuf.peers, flag_peers, [(qc, False, q_off, n_o * es)], pm.SLOT_FWD_Q, e, skip_self=True)
+            # by the copy engines: they need no SM, so they make progress whatever kernel fills the GPU (a store
+            # kernel queued behind a compute kernel that waits for the peer's stores would never start)
+            ops.p2p_push(qbuf.peers, flag_peers, [(qc, False, q_off, n_o * es)], pm.SLOT_FWD_Q, e, skip_self=True,
+                         dma=_PUSH_DMA)
             pushed = torch.cuda.Event()
             pushed.record(side)
+        if not _PUSH_DMA:
+            main.wait_event(pushed)             # a store kernel must have run before the kernel that waits for peers
         wait = (my_flags, pm.SLOT_FWD_Q, e, rank) if dt != torch.float32 else None
         if wait is None:
             ops.p2p_wait(my_flags, W, pm.SLOT_FWD_Q, e)
@@ -199,7 +205,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         o_recv = _carve(pbuf.local, p_off, (W, B, Hq, Sq, D), torch.float32)
         l_recv = _carve(pbuf.local, p_off + W * n_o * 4, (W, B * Hq, Sq), torch.float32)
         ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
-        main.wait_event(pushed)                 # the caller may reuse q once this call's kernels are done
+        main.wait_event(pushed)                 # the caller may reuse q once this call's work is done
         pm.status_watch.post()
         return q, k, v, o, L
     if sched == "p2p_pull":
@@ -366,13 +372,15 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             side.wait_event(ready)
             ops.p2p_push(ibuf.peers, flag_peers, [(qc, False, offs[0], n_q * es), (doc, False, offs[1], n_q * es),
                                                   (Lc, False, offs[2], n_r * 4), (delta, False, offs[3], n_r * 4)],
-                         pm.SLOT_BWD_IN, e, skip_self=True)
+                         pm.SLOT_BWD_IN, e, skip_self=True, dma=_PUSH_DMA)
             pushed = torch.cuda.Event()
             pushed.record(side)
         dq_parts = _carve(get_slabs("g_dq_send", W * n_q * 4, dev, 1)[0], 0, (W, B, Hq, Sq, D), torch.float32)
-        dq_parts.zero_()
+        dq_parts.zero_()                        # overlaps the stores on the side stream
         dk = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
         dv = torch.empty(B, Hkv, Skv, D, dtype=dt, device=dev)
+        if not _PUSH_DMA:
+            main.wait_event(pushed)             # see _attn_forward
         wait = (my_flags, pm.SLOT_BWD_IN, e, rank) if dt != torch.float32 else None
         if wait is None:
             ops.p2p_wait(my_flags, W, pm.SLOT_BWD_IN, e)

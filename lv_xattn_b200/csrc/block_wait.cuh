@@ -11,11 +11,13 @@ inline BlockWait make_block_wait(const lvx_block_wait* w, int q_blocks) {
   b.epoch = 0;
   b.first_blk = 0;
   b.limit = 0;
+  b.pipe_limit = LVX_SPIN_LIMIT_CYCLES;
   if (w != nullptr && w->my_flags != nullptr) {
     b.flags = w->my_flags + size_t(w->slot) * LVX_MAX_PEERS;
     b.epoch = w->epoch;
     b.first_blk = w->first_block;
     b.limit = p2p_wait_limit_cycles();
+    b.pipe_limit = LVX_SPIN_LIMIT_CYCLES + b.limit;
   } else if (w != nullptr) {
     b.first_blk = w->first_block;      // block order only, nothing to wait for
   }

@@ -224,7 +224,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         if (j + 2 < ntot) stat_after = fetch_stat(j + 2);
         if (warp == 0) BWD_TS(0, 0);
         // ---------------- P^T half: needs S^T only ----------------
-        if (!mbar_wait(&bars[BB_S_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL))) {
+        if (!mbar_wait(&bars[BB_S_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL), p.bw.pipe_limit)) {
           alive = false;
           break;
         }
@@ -236,7 +236,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[BB_X_LOADED]);
-        if (!mbar_wait(&bars[BB_STAT_FULL + (j & 1)], (j >> 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_STAT_FULL))) {
+        if (!mbar_wait(&bars[BB_STAT_FULL + (j & 1)], (j >> 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_STAT_FULL), p.bw.pipe_limit)) {
           alive = false;
           break;
         }
@@ -256,7 +256,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         if (warp == 0) BWD_TS(0, 2);
         // P^T overwrites S^T in X: wait until every warp has taken its S^T columns out.
-        if (!mbar_wait(&bars[BB_X_LOADED], j & 1, abort_flag, p.status, BWD_CODE(0, BB_X_LOADED))) {
+        if (!mbar_wait(&bars[BB_X_LOADED], j & 1, abort_flag, p.status, BWD_CODE(0, BB_X_LOADED), p.bw.pipe_limit)) {
           alive = false;
           break;
         }
@@ -266,7 +266,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[BB_P_FULL]);      // dV of this tile may start
         // ---------------- dS^T half: needs dP^T ----------------
-        if (!mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL))) {
+        if (!mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL), p.bw.pipe_limit)) {
           alive = false;
           break;
         }
@@ -295,7 +295,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         tc_fence_before();
         // dS^T row -> shared memory: two 64-column halves, each 128-byte swizzled (chunk ^ row%8). The
         // previous tile's dQ^T and dK products must have finished reading the buffer.
-        if (j > 0 && !mbar_wait(&bars[BB_DS_FREE], (j - 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_DS_FREE))) {
+        if (j > 0 && !mbar_wait(&bars[BB_DS_FREE], (j - 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_DS_FREE), p.bw.pipe_limit)) {
           alive = false;
           break;
         }
@@ -315,7 +315,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         stat_next = stat_after;
       }
       // ------------------------------- dK / dV epilogue -------------------------------
-      if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], 0, abort_flag, p.status, BWD_CODE(0, BB_ACC_DONE));
+      if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], 0, abort_flag, p.status, BWD_CODE(0, BB_ACC_DONE), p.bw.pipe_limit);
       tc_fence_after();
       if (alive) {
         const bool ok_row = (kv0 + r) < p.skv;
@@ -360,7 +360,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const int d = quarter * 32 + lane;                    // head-dim index = TMEM lane of dQ^T
       const uint32_t tY = tmem_base + TM_Y + (static_cast<uint32_t>(quarter * 32) << 16) + ch * 64;
       for (int j = 0; j < ntot; ++j) {
-        if (!mbar_wait(&bars[BB_DQ_FULL], j & 1, abort_flag, p.status, BWD_CODE(1, BB_DQ_FULL))) break;
+        if (!mbar_wait(&bars[BB_DQ_FULL], j & 1, abort_flag, p.status, BWD_CODE(1, BB_DQ_FULL), p.bw.pipe_limit)) break;
         tc_fence_after();
         if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 5);
         uint32_t v[2][32];
@@ -403,7 +403,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (!wait_block(p.bw, blk, abort_flag, p.status)) break;
             fence_async_global();
           }
-          if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY))) break;
+          if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY), p.bw.pipe_limit)) break;
           uint8_t* dstq = smem + BWD_OFF_Q + s * 2 * BWD_TILE;
           mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_TILE);
           for (int h = 0; h < 2; ++h) {
@@ -467,8 +467,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         umma_desc_join(ds_lo + ((kk * 2048) >> 4), HI), IDESC_DQ, kk > 0);
         };
 
-        bool ok = mbar_wait(&bars[BB_KV_FULL], 0, abort_flag, p.status, BWD_CODE(3, BB_KV_FULL));
-        ok = ok && mbar_wait(&bars[BB_Q_FULL + 0], 0, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL));
+        bool ok = mbar_wait(&bars[BB_KV_FULL], 0, abort_flag, p.status, BWD_CODE(3, BB_KV_FULL), p.bw.pipe_limit);
+        ok = ok && mbar_wait(&bars[BB_Q_FULL + 0], 0, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL), p.bw.pipe_limit);
         if (ok) {
           tc_fence_after();
           issue_st(tmem_base + TM_X, sK, sQ0);
@@ -482,7 +482,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           BWD_TS(1, 0);
           // dV needs P^T only, which is published before the dS^T half of the elementwise work; once dV has
           // read X, S^T of the next tile can go there, i.e. while the warps are still producing dS^T
-          ok = mbar_wait(&bars[BB_P_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_P_FULL));
+          ok = mbar_wait(&bars[BB_P_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_P_FULL), p.bw.pipe_limit);
           if (!ok) break;
           tc_fence_after();
           issue_acc(tmem_base + TM_DV, tmem_base + TM_X, sDO, j == 0);
@@ -490,14 +490,14 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int s1 = (j + 1) % BWD_NSQ;
           const uint32_t sQ1 = sQ0 + s1 * 2 * BWD_TILE;
           if (j + 1 < ntot) {
-            ok = mbar_wait(&bars[BB_Q_FULL + s1], ((j + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL));
+            ok = mbar_wait(&bars[BB_Q_FULL + s1], ((j + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL), p.bw.pipe_limit);
             if (!ok) break;
             tc_fence_after();
             issue_st(tmem_base + TM_X, sK, sQ1);
             tc_commit(&bars[BB_S_FULL]);
             BWD_TS(1, 2);
           }
-          ok = mbar_wait(&bars[BB_PDS_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL));
+          ok = mbar_wait(&bars[BB_PDS_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL), p.bw.pipe_limit);
           if (!ok) break;
           tc_fence_after();
           BWD_TS(1, 3);
@@ -508,7 +508,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           tc_commit(&bars[BB_DS_FREE]);
           BWD_TS(1, 4);
           if (j + 1 < ntot) {
-            ok = mbar_wait(&bars[BB_DQ_FREE], j & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE));
+            ok = mbar_wait(&bars[BB_DQ_FREE], j & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE), p.bw.pipe_limit);
             if (!ok) break;
             tc_fence_after();
             BWD_TS(1, 5);

@@ -146,7 +146,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       float m = -INFINITY, l = 0.f;
       bool alive = true;
       for (int j = 0; j < n; ++j) {
-        if (!mbar_wait(&bars[FB_S_FULL + wg], j & 1, abort_flag, p.status, FWD_CODE(wg, FB_S_FULL))) {
+        if (!mbar_wait(&bars[FB_S_FULL + wg], j & 1, abort_flag, p.status, FWD_CODE(wg, FB_S_FULL), p.bw.pipe_limit)) {
           alive = false;
           break;
         }
@@ -279,7 +279,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       }
       // ------------------------------- epilogue -------------------------------
       const int row = mb * 256 + wg * 128 + row_in_tile;
-      if (alive) alive = mbar_wait(&bars[FB_O_DONE + wg], 0, abort_flag, p.status, FWD_CODE(wg, FB_O_DONE));
+      if (alive) alive = mbar_wait(&bars[FB_O_DONE + wg], 0, abort_flag, p.status, FWD_CODE(wg, FB_O_DONE), p.bw.pipe_limit);
       tc_fence_after();
       if (alive) {
         const size_t prow = (size_t(bh) * p.nsplit + split) * p.rows + row;
@@ -318,12 +318,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           const int s = j % FWD_NS;
           const uint32_t ph = (j / FWD_NS) & 1;
           const int y = (tile0 + j) * 128;
-          if (!mbar_wait(&bars[FB_K_EMPTY + s], ph ^ 1, abort_flag, p.status, FWD_CODE(2, FB_K_EMPTY))) break;
+          if (!mbar_wait(&bars[FB_K_EMPTY + s], ph ^ 1, abort_flag, p.status, FWD_CODE(2, FB_K_EMPTY), p.bw.pipe_limit)) break;
           mbar_arrive_expect_tx(&bars[FB_K_FULL + s], FWD_TILE_BYTES);
           tma_load_3d(smem + FWD_OFF_K + s * FWD_TILE_BYTES, &tmK, &bars[FB_K_FULL + s], 0, y, kvs);
           tma_load_3d(smem + FWD_OFF_K + s * FWD_TILE_BYTES + FWD_HALF_BYTES, &tmK, &bars[FB_K_FULL + s], 64, y, kvs);
           k_issued = j + 1;
-          if (!mbar_wait(&bars[FB_V_EMPTY + s], ph ^ 1, abort_flag, p.status, FWD_CODE(2, FB_V_EMPTY))) break;
+          if (!mbar_wait(&bars[FB_V_EMPTY + s], ph ^ 1, abort_flag, p.status, FWD_CODE(2, FB_V_EMPTY), p.bw.pipe_limit)) break;
           mbar_arrive_expect_tx(&bars[FB_V_FULL + s], FWD_TILE_BYTES);
           tma_load_3d(smem + FWD_OFF_V + s * FWD_TILE_BYTES, &tmV, &bars[FB_V_FULL + s], 0, y, kvs);
           tma_load_3d(smem + FWD_OFF_V + s * FWD_TILE_BYTES + FWD_HALF_BYTES, &tmV, &bars[FB_V_FULL + s], 64, y, kvs);
@@ -383,8 +383,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           __syncwarp();
         };
 
-        bool ok = mbar_wait(&bars[FB_Q_FULL], 0, abort_flag, p.status, FWD_CODE(3, FB_Q_FULL));
-        ok = ok && mbar_wait(&bars[FB_K_FULL + 0], 0, abort_flag, p.status, FWD_CODE(3, FB_K_FULL));
+        bool ok = mbar_wait(&bars[FB_Q_FULL], 0, abort_flag, p.status, FWD_CODE(3, FB_Q_FULL), p.bw.pipe_limit);
+        ok = ok && mbar_wait(&bars[FB_K_FULL + 0], 0, abort_flag, p.status, FWD_CODE(3, FB_K_FULL), p.bw.pipe_limit);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
           tc_fence_after();
@@ -403,9 +403,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
           for (int i = 0; i < 2; ++i) {
             if (!ok) break;
             FWD_TS(2, i * 4 + 0);
-            ok = mbar_wait(&bars[FB_P_FULL + i], j & 1, abort_flag, p.status, FWD_CODE(3, FB_P_FULL));
+            ok = mbar_wait(&bars[FB_P_FULL + i], j & 1, abort_flag, p.status, FWD_CODE(3, FB_P_FULL), p.bw.pipe_limit);
             FWD_TS(2, i * 4 + 1);
-            if (ok && i == 0) ok = mbar_wait(&bars[FB_V_FULL + s], ph, abort_flag, p.status, FWD_CODE(3, FB_V_FULL));
+            if (ok && i == 0) ok = mbar_wait(&bars[FB_V_FULL + s], ph, abort_flag, p.status, FWD_CODE(3, FB_V_FULL), p.bw.pipe_limit);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
@@ -414,7 +414,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (i == 1) commit(&bars[FB_V_EMPTY + s]);
             if (j + 1 < n) {
               if (i == 0) {
-                ok = mbar_wait(&bars[FB_K_FULL + s1], ph1, abort_flag, p.status, FWD_CODE(3, FB_K_FULL));
+                ok = mbar_wait(&bars[FB_K_FULL + s1], ph1, abort_flag, p.status, FWD_CODE(3, FB_K_FULL), p.bw.pipe_limit);
                 ok = __all_sync(0xffffffffu, ok);
               }
               if (!ok) break;

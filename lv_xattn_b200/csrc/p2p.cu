@@ -428,6 +428,48 @@ int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_se
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);
 }
 
+int lvx_p2p_push_dma(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_segment* segments, int nseg, int slot,
+                     uint32_t epoch, int skip_self, void* stream) {
+  const char* who = "lvx_p2p_push_dma";
+  int rc = peers_ok(dst, who);
+  if (rc) return rc;
+  if ((rc = peers_ok(flags, who))) return rc;
+  if (flags->world != dst->world || flags->rank != dst->rank) return fail(LVX_ERR_SHAPE, "%s: the two peer tables disagree", who);
+  if (!segments || nseg < 1 || nseg > LVX_P2P_MAX_SEGMENTS) return fail(LVX_ERR_SHAPE, "%s: 1..%d segments", who, LVX_P2P_MAX_SEGMENTS);
+  if (slot < 0 || slot >= LVX_P2P_SLOTS) return fail(LVX_ERR_SHAPE, "%s: slot %d out of range", who, slot);
+  if ((rc = range_ok(flags, 0, sizeof(uint32_t) * LVX_P2P_SLOTS * LVX_MAX_PEERS, who, "the flag array"))) return rc;
+  const int world = dst->world, rank = dst->rank;
+  for (int g = 0; g < nseg; ++g) {
+    const lvx_push_segment& u = segments[g];
+    if (!u.src) return fail(LVX_ERR_NULL, "%s: segment %d has no source", who, g);
+    if ((rc = range_ok(dst, u.dst_offset + size_t(world - 1) * u.dst_rank_stride, u.bytes, who, "a segment's destination")))
+      return rc;
+    if (u.src_bytes && (u.src_stride ? size_t(world - 1) * u.src_stride + u.bytes : u.bytes) > u.src_bytes)
+      return fail(LVX_ERR_LIMIT, "%s: segment %d reads past its %zu-byte source", who, g, size_t(u.src_bytes));
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Peer by peer, starting after this rank (so that at any moment the ranks write to different peers): the data
+  // copies, then the 4-byte epoch. Copies of one stream run in order, so the epoch lands after the data.
+  for (int step = 0; step < world; ++step) {
+    const int s = (rank + 1 + step) % world;
+    if (!(skip_self && s == rank)) {
+      for (int g = 0; g < nseg; ++g) {
+        const lvx_push_segment& u = segments[g];
+        if (u.bytes == 0) continue;
+        uint8_t* d = const_cast<uint8_t*>(static_cast<const uint8_t*>(dst->ptr[s])) + u.dst_offset + size_t(rank) * u.dst_rank_stride;
+        const uint8_t* src = static_cast<const uint8_t*>(u.src) + size_t(s) * u.src_stride;
+        cudaError_t e = cudaMemcpyAsync(d, src, u.bytes, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return cuda_fail(e, "lvx_p2p_push_dma: data copy");
+      }
+    }
+    uint32_t* f = reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(static_cast<const uint8_t*>(flags->ptr[s]))) + slot * LVX_MAX_PEERS + rank;
+    // the source is a host variable: the runtime stages it before the call returns
+    cudaError_t e = cudaMemcpyAsync(f, &epoch, sizeof(uint32_t), cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return cuda_fail(e, "lvx_p2p_push_dma: epoch copy");
+  }
+  return LVX_OK;
+}
+
 int lvx_p2p_wait(const uint32_t* my_flags, int world, int slot, uint32_t epoch, void* stream) {
   const char* who = "lvx_p2p_wait";
   if (!my_flags) return fail(LVX_ERR_NULL, "%s: null flag array", who);

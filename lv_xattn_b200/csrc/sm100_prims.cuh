@@ -53,8 +53,9 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 // Bounded wait. `abort_flag` lives in shared memory and is set by whichever thread of the CTA
 // first runs out of time, so that every other waiter leaves at once instead of timing out in turn.
 // Returns true when the barrier phase completed, false when the CTA is aborting.
+// `limit`: cycles; kernels whose producer may itself be waiting for another GPU pass a longer one.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, long long limit = LVX_SPIN_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
@@ -62,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > LVX_SPIN_LIMIT_CYCLES) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;
@@ -82,7 +83,9 @@ struct BlockWait {
   const uint32_t* flags;     // this GPU's flag words of the slot, one per rank
   uint32_t epoch;
   int first_blk;             // block processed first (this rank's own)
-  long long limit;           // cycles
+  long long limit;           // cycles a block may be late
+  long long pipe_limit;      // limit of the CTA's own pipeline waits: the usual one, plus `limit` when a producer
+                             // may legitimately sit in wait_block (everything downstream of it waits that long too)
 };
 // Returns false when the block did not arrive in time (the status word then holds 0x1300 | blk).
 __device__ __forceinline__ bool wait_block(const BlockWait& w, int blk, volatile int* abort_flag, int* status) {

@@ -393,11 +393,12 @@ def p2p_sum_cast(parts_peers, offset: int, out, my_flags, slot: int, epoch: int)
     _count()
 
 
-def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int, skip_self: bool = False):
+def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int, skip_self: bool = False, dma: bool = False):
     """One launch: for every rank s and every segment (src tensor, all_to_all, dst_offset, dst_rank_stride),
     copies src (all_to_all False: the whole tensor to everyone; True: its block s, src being [W, ...]) into rank
     s's buffer at dst_offset + rank*dst_rank_stride, then publishes `epoch` for `slot` to every rank.
-    skip_self: this rank's own buffer is not written (the caller fills it), the epoch still goes to everyone."""
+    skip_self: this rank's own buffer is not written (the caller fills it), the epoch still goes to everyone.
+    dma: the copies are done by the copy engines (lvx_p2p_push_dma), which need no SM."""
     lib = _lib.load()
     W = dst_peers.world
     arr = (_lib.LvxPushSegment * len(segments))()
@@ -414,10 +415,12 @@ def p2p_push(dst_peers, flags_peers, segments, slot: int, epoch: int, skip_self:
         arr[i].dst_rank_stride = dst_rank_stride
         arr[i].bytes = nbytes
         arr[i].src_bytes = total
-    _lib.check(lib.lvx_p2p_push(ctypes.byref(dst_peers), ctypes.byref(flags_peers), arr, len(segments), slot,
-                                ctypes.c_uint32(epoch & 0xFFFFFFFF), 1 if skip_self else 0, _lib.stream_ptr()),
-               "lvx_p2p_push")
-    _count()
+    fn = lib.lvx_p2p_push_dma if dma else lib.lvx_p2p_push
+    _lib.check(fn(ctypes.byref(dst_peers), ctypes.byref(flags_peers), arr, len(segments), slot,
+                  ctypes.c_uint32(epoch & 0xFFFFFFFF), 1 if skip_self else 0, _lib.stream_ptr()),
+               "lvx_p2p_push_dma" if dma else "lvx_p2p_push")
+    if not dma:
+        _count()
 
 
 def p2p_wait(my_flags, world: int, slot: int, epoch: int):

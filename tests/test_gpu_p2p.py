@@ -101,6 +101,19 @@ def test_push_all_gather_and_all_to_all(dev, world):
         for r in range(world):
             assert torch.equal(recv[r][par, 0], torch.stack(own))
             assert torch.equal(recv[r][par, 1], torch.stack([parts[c][r] for c in range(world)]))
+    # the same exchange by the copy engines (lvx_p2p_push_dma)
+    recv3 = [torch.zeros(2, world, n, device=dev) for _ in range(world)]
+    own = [torch.randn(n, device=dev) for _ in range(world)]
+    parts = [torch.randn(world, n, device=dev) for _ in range(world)]
+    for r in range(world):
+        ops.p2p_push(_peers(recv3, r), _peers(flags, r), [(own[r], False, 0, n * 4), (parts[r], True, world * n * 4, n * 4)],
+                     7, 1, dma=True)
+    for r in range(world):
+        ops.p2p_wait(flags[r], world, 7, 1)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(recv3[r][0], torch.stack(own))
+        assert torch.equal(recv3[r][1], torch.stack([parts[c][r] for c in range(world)]))
     # skip_self: the peers are written, this rank's own buffer is left to the caller, the epoch reaches everyone
     recv2 = [torch.zeros(world, n, device=dev) for _ in range(world)]
     own = [torch.randn(n, device=dev) for _ in range(world)]

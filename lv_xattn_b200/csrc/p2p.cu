@@ -103,26 +103,25 @@ p2p_gather_kernel(PeerPtrs src, size_t src_offset, size_t bytes, uint8_t* __rest
                   const uint32_t* my_flags, int slot, uint32_t epoch, int* status, long long limit) {
   if (!p2p_wait_all(my_flags, world, slot, epoch, status, limit)) return;
   const size_t n16 = bytes >> 4;
-  const size_t total = n16 * world;
   const size_t gstride = size_t(gridDim.x) * blockDim.x;
-  // loads over NVLink are round trips: four in flight per thread
-  for (size_t i0 = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * gstride) {
-    float4 v[4];
-    uint8_t* d[4];
+  const size_t gtid = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  // source by source (no index division in the copy loop); loads over NVLink are round trips: four in flight per thread
+  for (int s = 0; s < world; ++s) {
+    const uint8_t* from = src.p[s] + src_offset;
+    uint8_t* to = dst + size_t(s) * dst_stride;
+    for (size_t i0 = gtid; i0 < n16; i0 += 4 * gstride) {
+      float4 v[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const size_t i = i0 + size_t(u) * gstride;
-      d[u] = nullptr;
-      if (i < total) {
-        const int s = int(i / n16);
-        const size_t off = (i - size_t(s) * n16) << 4;
-        v[u] = ld_cg_f4(src.p[s] + src_offset + off);
-        d[u] = dst + size_t(s) * dst_stride + off;
+      for (int u = 0; u < 4; ++u) {
+        const size_t i = i0 + size_t(u) * gstride;
+        if (i < n16) v[u] = ld_cg_f4(from + (i << 4));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const size_t i = i0 + size_t(u) * gstride;
+        if (i < n16) reinterpret_cast<float4*>(to)[i] = v[u];
       }
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      if (d[u]) *reinterpret_cast<float4*>(d[u]) = v[u];
   }
 }
 
@@ -226,27 +225,26 @@ p2p_push_kernel(PeerPtrs dst, PeerPtrs flags, PushArgs a, int world, int rank, i
   for (int g = 0; g < a.nseg; ++g) {
     const PushSeg sg = a.seg[g];
     const size_t n16 = sg.bytes >> 4;
-    const size_t total = n16 * world;
-    // four 16-byte chunks per thread and round, all loads issued before the first (posted) store, so that the
-    // copy is bound by the link and not by one load-store round trip at a time
-    for (size_t i0 = gtid; i0 < total; i0 += 4 * gstride) {
-      float4 v[4];
-      uint8_t* d[4];
+    // destination by destination (no index division in the copy loop); four 16-byte chunks per thread and round,
+    // all loads issued before the first (posted) store, so that the copy is bound by the link and not by one
+    // load-store round trip at a time
+    for (int r = 0; r < world; ++r) {
+      if (a.skip_self && r == rank) continue;
+      const uint8_t* src = sg.src + size_t(r) * sg.src_stride;
+      uint8_t* d = const_cast<uint8_t*>(dst.p[r]) + sg.dst_offset + size_t(rank) * sg.dst_rank_stride;
+      for (size_t i0 = gtid; i0 < n16; i0 += 4 * gstride) {
+        float4 v[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const size_t i = i0 + size_t(u) * gstride;
-        d[u] = nullptr;
-        if (i < total) {
-          const int r = int(i / n16);
-          if (a.skip_self && r == rank) continue;
-          const size_t off = (i - size_t(r) * n16) << 4;
-          v[u] = *reinterpret_cast<const float4*>(sg.src + size_t(r) * sg.src_stride + off);
-          d[u] = const_cast<uint8_t*>(dst.p[r]) + sg.dst_offset + size_t(rank) * sg.dst_rank_stride + off;
+        for (int u = 0; u < 4; ++u) {
+          const size_t i = i0 + size_t(u) * gstride;
+          if (i < n16) v[u] = reinterpret_cast<const float4*>(src)[i];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const size_t i = i0 + size_t(u) * gstride;
+          if (i < n16) reinterpret_cast<float4*>(d)[i] = v[u];
         }
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (d[u]) *reinterpret_cast<float4*>(d[u]) = v[u];
     }
   }
   __threadfence_system();
@@ -329,7 +327,7 @@ int lvx_p2p_gather(const lvx_peers* src, size_t src_offset, size_t bytes, void* 
   int* status = device_status_ptr();
   if (!status) return fail(LVX_ERR_DRIVER, "%s: no device status word", who);
   if (bytes == 0) return LVX_OK;
-  p2p_gather_kernel<<<grid_for((bytes >> 4) * src->world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  p2p_gather_kernel<<<grid_for(((bytes >> 4) + 3) / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       to_dev(src), src_offset, bytes, static_cast<uint8_t*>(dst), dst_stride, src->world, my_flags, slot, epoch, status,
       wait_limit_cycles());
   cudaError_t e = cudaGetLastError();
@@ -422,7 +420,7 @@ int lvx_p2p_push(const lvx_peers* dst, const lvx_peers* flags, const lvx_push_se
     a.seg[g].bytes = u.bytes;
     if (u.bytes > most) most = u.bytes;
   }
-  p2p_push_kernel<<<grid_for((most >> 4) * dst->world), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  p2p_push_kernel<<<grid_for(((most >> 4) + 3) / 4), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       to_dev(dst), to_dev(flags), a, dst->world, dst->rank, slot, epoch);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? LVX_OK : cuda_fail(e, who);

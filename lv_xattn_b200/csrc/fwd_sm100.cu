@@ -172,19 +172,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
               float x0, x1, x2, x3;
               f32x2_get(fma2(f32x2(s0, s1), c2, nm2), x0, x1);
               f32x2_get(fma2(f32x2(s2, s3), c2, nm2), x2, x3);
-#ifdef LVX_FWD_PACKED_EXP
-              if (IS_BF16) {
-                // exponent pairs on the MUFU in packed bf16: the argument is rounded to bf16 first (its error is
-                // 2^-9 relative, i.e. largest for the terms that weigh least), P comes out in the MMA's own format,
-                // and the row sum is taken from exactly the values the MMA will use
-                const uint32_t pa = ex2_bf16x2(pack_bf16x2(x0, x1)), pb = ex2_bf16x2(pack_bf16x2(x2, x3));
-                sum_a = add2(sum_a, f32x2(__uint_as_float(pa << 16), __uint_as_float(pa & 0xffff0000u)));
-                sum_b = add2(sum_b, f32x2(__uint_as_float(pb << 16), __uint_as_float(pb & 0xffff0000u)));
-                out[2 * i] = pa;
-                out[2 * i + 1] = pb;
-                continue;
-              }
-#endif
               const float e0 = ex2f(x0), e1 = ex2f(x1), e2 = ex2f(x2), e3 = ex2f(x3);
               sum_a = add2(sum_a, f32x2(e0, e1));
               sum_b = add2(sum_b, f32x2(e2, e3));

@@ -9,6 +9,10 @@ reference benchmark's distributions, test.py:101-107: q,k,v ~ N(0,0.5^2), dO ~ N
   config 2 (default, the headline)  B=1, Hq=32, Hkv=8, D=128, Sq=2048 text queries, Skv=131072 visual keys, bf16
   config 1  the reference's CPU-runnable correctness shape: Sq=512, Skv=8192, fp32 (exact FP32-FMA kernels)
   config 5  long-visual stress: B=2, Sq=256, Skv=1048576, key padding to 1048576 / 786432 valid keys, bf16
+  config 4  end-to-end training step (forward, loss, backward, gradient all-reduce; no optimizer, as in the reference's
+            driver test_llama3.py:710-737) of a random-init Llama-3.2-11B-Vision-shaped text decoder: 40 layers, gated
+            cross-attention at 3,8,...,38, hidden 4096, FFN 14336, vocab 128256, 2048 tokens, visual states
+            [1,262144,4096]; both Hugging Face hooks installed, text and visual sequences sharded over the ranks
   config 3  Llama-3.2-11B-Vision-shaped cross-attention block (hidden 4096, per-head RMSNorm on q and k, q/k/v/o
             projections N(0,0.02^2), states [1,409856,4096], text [1,1024,4096], bf16) through the
             patch_cross_attention_forward hook with K/V recomputed in backward
@@ -50,6 +54,8 @@ CONFIGS = {
     1: dict(B=1, Hq=32, Hkv=8, D=128, Sq=512, Skv=8192, dtype="f32", valid=None),
     2: dict(B=1, Hq=32, Hkv=8, D=128, Sq=2048, Skv=131072, dtype="bf16", valid=None),
     3: dict(B=1, Hq=32, Hkv=8, D=128, Sq=1024, Skv=409856, dtype="bf16", valid=None, hidden=4096, layer=True),
+    4: dict(B=1, Hq=32, Hkv=8, D=128, Sq=2048, Skv=262144, dtype="bf16", valid=None, hidden=4096, decoder=True,
+            layers=40, cross_layers=list(range(3, 40, 5)), ffn=14336, vocab=128256),
     5: dict(B=2, Hq=32, Hkv=8, D=128, Sq=256, Skv=1048576, dtype="bf16", valid=[1048576, 786432]),
 }
 TORCH_DTYPE = {"bf16": torch.bfloat16, "f32": torch.float32}
@@ -188,6 +194,9 @@ def workload_name(cid, cfg):
         s += f" kv_valid_len={cfg['valid']}"
     if cfg.get("layer"):
         s += f" Llama-3.2-11B-Vision cross-attention block (hidden {cfg['hidden']}, K/V recomputed in backward)"
+    if cfg.get("decoder"):
+        s += (f" per cross layer; {cfg['layers']}-layer Llama-3.2-11B-Vision-shaped text decoder, cross-attention layers "
+              f"{cfg['cross_layers']}, hidden {cfg['hidden']}, training step without optimizer")
     return s + ", Q and K/V sharded by sequence"
 
 
@@ -461,6 +470,179 @@ def run_layer(args, cfg, rank, world, local, dev):
     return parity is None or parity["ok"]
 
 
+def run_decoder(args, cfg, rank, world, local, dev):
+    """Config 4: a training step of the whole text decoder with both hooks installed (hf_patch.install_hooks, as the
+    reference assigns them at test_llama3.py:666-667). Random-init weights N(0,0.02^2), norm weights 1, the
+    cross-attention gates 0.25 (the stock init of 0 would switch the cross-attention layers off), token ids and labels
+    uniform, visual states N(0,1) generated shard-wise: synthetic stand-ins for the reference's real-model run
+    (test_llama3.py:657-770). The weights are replicated; every rank differentiates its shard of the sequence and the
+    gradients are summed with an NCCL all-reduce inside the timed step. Returns False when the loss is not finite."""
+    import lv_xattn_b200 as lvx
+    from lv_xattn_b200 import _lib, hf_patch, ops
+    from transformers.models.mllama import modeling_mllama as mllama
+
+    Hq, Hkv, D, Sq, Skv, hid = (cfg[n] for n in ("Hq", "Hkv", "D", "Sq", "Skv", "hidden"))
+    layers = args.layers or cfg["layers"]
+    cross = [i for i in cfg["cross_layers"] if i < layers]
+    Sl, Kl = Sq // world, Skv // world
+    mcfg = mllama.MllamaTextConfig(hidden_size=hid, num_attention_heads=Hq, num_key_value_heads=Hkv,
+                                   num_hidden_layers=layers, intermediate_size=cfg["ffn"], vocab_size=cfg["vocab"],
+                                   cross_attention_layers=cross, max_position_embeddings=max(Sq, 4096), pad_token_id=0)
+    mcfg._attn_implementation = "eager"
+    with torch.device("meta"):
+        model = mllama.MllamaForCausalLM(mcfg)
+    model = model.to_empty(device=dev).to(torch.bfloat16)
+    gw = torch.Generator(device=dev).manual_seed(4321)          # the same weights on every rank
+    with torch.no_grad():
+        for name, p in model.named_parameters():
+            if "gate" in name:
+                p.fill_(0.25)
+            elif "norm" in name:
+                p.fill_(1.0)
+            else:
+                p.copy_(torch.empty(p.shape, device=dev).normal_(0, 0.02, generator=gw))
+        for name, b in model.named_buffers():               # rotary tables were allocated on the meta device
+            if "inv_freq" in name:
+                rope = mllama.MllamaRotaryEmbedding(mcfg, device=dev)
+                b.copy_(rope.inv_freq)
+    n_params = sum(p.numel() for p in model.parameters())
+    hf_patch.install_hooks("lv_xattn")
+    g = torch.Generator(device=dev).manual_seed(5000 + rank)
+    ids = torch.randint(1, cfg["vocab"], (1, Sl), device=dev, generator=g)
+    labels = torch.randint(1, cfg["vocab"], (1, Sl), device=dev, generator=g)
+    states = torch.empty(1, Kl, hid, device=dev).normal_(0, 1, generator=g).bfloat16()
+    pos = (torch.arange(Sl, device=dev) + rank * Sl)[None]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    params = [p for p in model.parameters()]
+
+    def step(ids_=None, states_=None):
+        for p in params:
+            p.grad = None
+        h = model.model(input_ids=ids if ids_ is None else ids_, position_ids=pos, use_cache=False,
+                        cross_attention_states=states if states_ is None else states_).last_hidden_state
+        logits = model.lm_head(h).float()
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), labels.view(-1), reduction="sum") / Sq
+        loss.backward()
+        if world > 1:                                  # replicated weights: sum the ranks' gradients
+            works = [dist.all_reduce(p.grad, async_op=True) for p in params if p.grad is not None]
+            for w in works:
+                w.wait()
+        return loss.detach()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        evs = []
+        for _ in range(steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            evs.append((a, b))
+        barrier()
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t[0].item()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    ops.set_profiling(True)
+    ops.launch_count = 0
+    n_before = len(sampler.samples)
+    total_ms = timed(step, args.steps, 0)
+    sampler.samples = sampler.samples[n_before:] or sampler.samples[-1:]
+    clocks = sampler.stop() if rank == 0 else None
+    launches = ops.launch_count
+    prof = ops.take_profile()
+    ops.set_profiling(False)
+    status = _lib.device_status()
+    if status != 0:
+        raise SystemExit(f"device status word {status:#x}: a bounded wait ran out")
+    ms = total_ms / args.steps
+    loss = step()
+    if world > 1:
+        dist.all_reduce(loss)
+    loss_v = loss.item()
+    nc = len(cross)
+    core = nc * 3.5 * 4.0 * Hq * D * Sq * Skv
+    proj = nc * 3 * 2 * (2.0 * Skv * hid * Hkv * D)
+    dense = 6.0 * (n_params - cfg["vocab"] * hid) * Sq            # embedding lookup does no FLOPs; the head does
+    self_attn = (layers - nc) * 3.5 * 4.0 * Hq * D * Sq * Sq / 2
+    flops = core + proj + dense + self_attn
+    pk = peaks()
+    bwd_ms, fwd_ms = sum(prof["bwd"]) / args.steps, sum(prof["fwd"]) / args.steps
+    proj_ms = sum(prof.get("proj", [])) / args.steps
+    achieved = (core * 2.5 / 3.5 / world) / (bwd_ms * 1e-3) / 1e12 if bwd_ms > 0 else 0.0
+    roofline = {"bound": "tensor", "kernel": "bwd_kernel", "achieved": achieved, "peak": pk["bf16_sustained"],
+                "unit": "TFLOP/s", "frac": achieved / pk["bf16_sustained"],
+                "peak_source": f"{pk['source']} (sustained cuBLAS bf16)", "traffic": None,
+                "bwd_kernel_ms_per_step": bwd_ms, "fwd_kernel_ms_per_step": fwd_ms,
+                "kv_projection_kernel_ms_per_step": proj_ms,
+                "cross_attention_core_ms_per_step": bwd_ms + fwd_ms,
+                "ms_per_cross_layer_core": (bwd_ms + fwd_ms) / max(nc, 1)}
+    parity = {"loss": loss_v, "ok": bool(math.isfinite(loss_v)), "rel_max": None,
+              "checked": ("loss finite (ln(vocab) = %.3f for random weights). Sharded-versus-unsharded parity of the whole "
+                          "decoder through both hooks is tests/test_decoder_cpu.py (two gloo ranks, every parameter's "
+                          "gradient); the hooks with the real kernels are tests/test_gpu_hf_patch.py and "
+                          "tests/test_gpu_multi.py; no reference numbers exist for this configuration" % math.log(cfg["vocab"]))}
+
+    e2e = None
+    if not args.no_e2e:
+        hids, hst = ids.cpu().pin_memory(), states.cpu().pin_memory()
+        hloss = torch.empty((), dtype=torch.float32).pin_memory()
+
+        def step_e2e():
+            l_ = step(hids.to(dev, non_blocking=True), hst.to(dev, non_blocking=True))
+            hloss.copy_(l_, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        e_steps = max(1, min(args.steps, 3))
+        e_ms = timed(step_e2e, e_steps, 1)
+        e2e = {"value": flops / (e_ms / e_steps * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e_ms / e_steps,
+               "h2d_bytes_per_step": world * (hids.numel() * 8 + hst.numel() * 2), "d2h_bytes_per_step": world * 4,
+               "steps": e_steps}
+    hf_patch.uninstall_hooks()
+    hf_patch.clear_global_cross_attention_states()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        tf, dt, desc = cpu_attention_sample(cfg, threads, cpu_sample_heads(cfg, True))
+        cpu = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc + " (cross-attention core only)",
+               "seconds": dt}
+    if rank == 0:
+        value = flops / (ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(args.config, cfg), "layers": layers, "parameters": n_params,
+                       "l2": "256 MB buffer written between timed steps",
+                       "schedule": "single GPU" if world == 1 else lvx.attn._schedule(None, states),
+                       "flops": {"cross_attention_core": core, "kv_projections": proj, "dense_layers_and_head": dense,
+                                 "self_attention": self_attn},
+                       "timing": "CUDA events per step on the launch stream, summed; max over ranks"},
+            "ms_per_layer": (bwd_ms + fwd_ms + proj_ms) / max(nc, 1), "tflops_per_gpu": value / world,
+            "frac_of_tensor_roofline": (flops / world / (pk["bf16_sustained"] * 1e12) * 1e3) / ms,
+            "roofline": roofline, "parity": parity, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    return parity["ok"]
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -468,6 +650,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=2, choices=sorted(CONFIGS))
+    ap.add_argument("--layers", type=int, default=None, help="config 4 only: fewer decoder layers (a smoke run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -500,6 +683,13 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         lvx.initialize_distributed("nccl")
 
+    if cfg.get("decoder"):
+        ok = run_decoder(args, cfg, rank, world, local, dev)
+        if world > 1:
+            dist.destroy_process_group()
+        if not ok:
+            raise SystemExit("config 4: loss not finite")
+        return
     if cfg.get("layer"):
         ok = run_layer(args, cfg, rank, world, local, dev)
         if world > 1:

@@ -24,9 +24,11 @@ from .attn import (  # noqa: F401
 from .hf_patch import (  # noqa: F401,E402
     clear_global_cross_attention_states,
     get_global_cross_attention_states,
+    install_hooks,
     patch_cross_attention_forward,
     patch_self_attention_forward,
     set_global_cross_attention_states,
+    uninstall_hooks,
 )
 from .host_io import HostStreamedAttention  # noqa: F401,E402
 from .peer_memory import check_device_status  # noqa: F401,E402

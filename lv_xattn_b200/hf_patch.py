@@ -165,3 +165,25 @@ def patch_self_attention_forward(attention_mode="lv_xattn"):
         return self.o_proj(out), None
 
     return forward
+
+
+_SAVED_FORWARDS = {}
+
+
+def install_hooks(attention_mode="lv_xattn"):
+    """Assigns the two hooks onto the installed transformers' Mllama text attention classes, as the reference's
+    driver does (test_llama3.py:666-667). Every MllamaTextCrossAttention / MllamaTextSelfAttention of every model in
+    the process is then sequence-parallel; `uninstall_hooks()` restores the stock forwards."""
+    from transformers.models.mllama import modeling_mllama as M
+    if not _SAVED_FORWARDS:
+        _SAVED_FORWARDS["cross"] = M.MllamaTextCrossAttention.forward
+        _SAVED_FORWARDS["self"] = M.MllamaTextSelfAttention.forward
+    M.MllamaTextCrossAttention.forward = patch_cross_attention_forward(attention_mode)
+    M.MllamaTextSelfAttention.forward = patch_self_attention_forward(attention_mode)
+
+
+def uninstall_hooks():
+    from transformers.models.mllama import modeling_mllama as M
+    if _SAVED_FORWARDS:
+        M.MllamaTextCrossAttention.forward = _SAVED_FORWARDS.pop("cross")
+        M.MllamaTextSelfAttention.forward = _SAVED_FORWARDS.pop("self")

@@ -121,6 +121,20 @@ def _build_bias(bias_func, local_bias_args, peer_bias_args, q, k):
     return bias.to(device=q.device, dtype=torch.float32)
 
 
+def _status_poll(t):
+    """Start of a call: raise if a kernel of an earlier call gave up on a bounded wait (see peer_memory.StatusWatch)."""
+    if t.is_cuda:
+        from .peer_memory import status_watch
+        status_watch.poll()
+
+
+def _status_post(t):
+    """End of a call: queue a look at the device status word behind the call's last kernel (no synchronisation)."""
+    if t.is_cuda:
+        from .peer_memory import status_watch
+        status_watch.post()
+
+
 def _carve(buf: torch.Tensor, offset: int, shape, dtype) -> torch.Tensor:
     n = 1
     for s in shape:
@@ -137,6 +151,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
     reference :294-296); the result is then the attention of the local Q block over the local K/V only.
     kv_valid_len: optional global number of valid K/V rows per batch entry (key padding)."""
     _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args)
+    _status_poll(q)
     W = get_sequence_parallel_size()
     B, Hq, Sq, D = q.shape
     dev, dt = q.device, q.dtype
@@ -151,6 +166,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         for _ in range(W):
             part = ops.fwd_partials(qc, kc, vc, sm_scale, kvl, bias=bias)
             ops.fwd_combine(part, None, None, o, L, True)
+        _status_post(q)
         return q, k, v, o, L
 
     n_o, n_l = B * Hq * Sq * D, B * Hq * Sq
@@ -248,6 +264,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         ops.fwd_combine(part, None, None, o_parts, l_parts.view(W * B * Hq, Sq), False)
         wait_async_handles(all_to_all_blocks([(o_parts, o_recv), (l_parts, l_recv)], comm_mode))
         ops.fwd_merge_parts(o_recv, l_recv, dt, o_out=o, lse_out=L)
+        _status_post(q)
         return q, k, v, o, L
 
     acc_bytes = n_o * 4 + n_l * 4
@@ -295,6 +312,7 @@ def _attn_forward(q, k, v, causal, sm_scale, comm_mode, bias_func=None, local_bi
         if not last:
             q_cur, args_cur = q_next, args_next
     wait_async_handles(acc_reqs)
+    _status_post(q)
     return q, k, v, o, L
 
 
@@ -316,6 +334,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
     """Returns (dq, dk, dv): dq like q, dk/dv like k/v (summed over the query heads of each KV group)
     (reference :437-545). `backward_engine` is accepted and ignored, as in the reference."""
     _check_common(q, k, v, causal, bias_func, local_bias_args, remote_bias_args)
+    _status_poll(q)
     W = get_sequence_parallel_size()
     B, Hq, Sq, D = q.shape
     Hkv, Skv = k.shape[1], k.shape[2]
@@ -341,6 +360,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
             dq_acc.zero_()
             ops.bwd_block(qc, doc, Lc, delta, kc, vc, sm_scale, dq_acc, dk, dv, "final", kvl, bias=bias)
         ops.add_cast(dq_acc, None, dt, out=dq)
+        _status_post(q)
         return dq, dk, dv
     if sched in ("p2p", "p2p_pull") and (n_r * 4) % 16:
         if (schedule or os.environ.get("LVX_SCHEDULE", _DEFAULT_SCHEDULE)) != "auto":
@@ -445,6 +465,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
                       dq_parts, dk, dv, "final", kvl)       # one pass: dK/dV leave the kernel in their final dtype
         wait_async_handles(all_to_all_blocks([(dq_parts, dq_recv)], comm_mode))
         ops.sum_cast(dq_recv, dt, out=dq)
+        _status_post(q)
         return dq, dk, dv
     else:
         slab_bytes = 2 * n_q * es + 2 * n_r * 4
@@ -512,6 +533,7 @@ def _attn_backward(do, q, k, v, o, L, causal, sm_scale, comm_mode, backward_engi
 
     dk = ops.add_cast(dk_acc, None, dt)
     dv = ops.add_cast(dv_acc, None, dt)
+    _status_post(q)
     return dq, dk, dv
 
 

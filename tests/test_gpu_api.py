@@ -131,3 +131,32 @@ def test_host_streamed_attention(cuda_device, chunks, valid):
         st.step(hq, hk, hv, hdo, SCALE, ho, hdq, hdk, hdv, kv_valid_len=valid)
     for name, got, r in zip(("o", "dq", "dk", "dv"), (ho, hdq, hdk, hdv), (ref[0], ref[2], ref[3], ref[4])):
         _parity.assert_close(got.float(), r, name, f"host_streamed_{chunks}", *_parity.BF16[name])
+
+
+def test_host_streamed_attention_pipelined(cuda_device):
+    """Three steps with DIFFERENT inputs, each prefetched while the one before is queued and none waited for until
+    the end: every step's results (its own host output tensors) match the oracle, so neither an input set nor an
+    output buffer was reused too early."""
+    import lv_xattn_b200 as lvx
+    B, Hq, Hkv, Sq, Skv = 1, 8, 2, 128, 1000
+    st = lvx.HostStreamedAttention(cuda_device, chunks=3)
+    steps = []
+    for seed in (31, 32, 33):
+        q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, seed, torch.bfloat16)
+        host = [t.pin_memory() for t in (q, k, v, do)]
+        outs = [torch.empty_like(host[0]).pin_memory(), torch.empty_like(host[0]).pin_memory(),
+                torch.empty_like(host[1]).pin_memory(), torch.empty_like(host[1]).pin_memory()]
+        steps.append((host, outs, orc.attention_fwd_bwd(q, k, v, do, SCALE, None)))
+    st.prefetch(*steps[0][0])
+    for i, (host, outs, _) in enumerate(steps):
+        if i + 1 < len(steps):
+            st.prefetch(*steps[i + 1][0])
+        st.step(*host, SCALE, *outs, wait=False)
+    with pytest.raises(RuntimeError):          # two sets at most
+        st.prefetch(*steps[0][0])
+        st.prefetch(*steps[1][0])
+        st.prefetch(*steps[2][0])
+    st.finish()
+    for i, (_, outs, ref) in enumerate(steps):
+        for name, got, r in zip(("o", "dq", "dk", "dv"), outs, (ref[0], ref[2], ref[3], ref[4])):
+            _parity.assert_close(got.float(), r, name, f"host_pipelined_step{i}", *_parity.BF16[name])

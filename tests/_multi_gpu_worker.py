@@ -36,6 +36,19 @@ for B, Hq, Hkv, Sq, Skv, dtype, valid in cases:
             from lv_xattn_b200 import ring
             _, _, _, o, L = ring._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid)
             dq, dk, dv = ring._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid)
+        elif sched == "hostio":     # pinned host shards through HostStreamedAttention, three pipelined steps (not first)
+            st = lvx.HostStreamedAttention(dev)
+            hin = [t.cpu().pin_memory() for t in (ql, kl, vl, dol)]
+            hout = [torch.empty_like(hin[0]).pin_memory(), torch.empty_like(hin[0]).pin_memory(),
+                    torch.empty_like(hin[1]).pin_memory(), torch.empty_like(hin[1]).pin_memory()]
+            st.prefetch(*hin)
+            for i in range(3):
+                if i < 2:
+                    st.prefetch(*hin)
+                st.step(*hin, scale, *hout, kv_valid_len=valid, wait=False)
+            st.finish()
+            o, dq, dk, dv = (t.to(dev) for t in hout)
+            L = first[1]
         else:
             _, _, _, o, L = lvx._attn_forward(ql, kl, vl, False, scale, None, kv_valid_len=valid, schedule=sched)
             dq, dk, dv = lvx._attn_backward(dol, ql, kl, vl, o, L, False, scale, None, "flash", kv_valid_len=valid,

@@ -42,3 +42,10 @@ def test_hf_hooks_on_gpu_ranks(world):
     """Both Hugging Face hooks with sharded sequences on GPU ranks (global-position causal mask, per-rank rotary
     slice, K/V recompute) against the unsharded stock modules."""
     _run(world, "gather", 29700 + world, extra=("hf",))
+
+
+@pytest.mark.parametrize("world", [2])
+def test_host_streamed_on_gpu_ranks(world):
+    """Pinned host shards in and out on every rank, consecutive steps pipelined, against the device-resident
+    schedule and the oracle."""
+    _run(world, "gather,hostio", 29750 + world)

@@ -9,9 +9,19 @@
 // is held to. fp32 is the correctness configuration, not the throughput one, so it gets straightforward
 // tiled kernels with the same interface, workspace layout and masking rules as the 16-bit tensor-core path.
 //
-// Both kernels use 64 x 64 score tiles and 256 threads laid out 16 x 16: thread (ty, tx) owns the 4 x 4 block
-// of scores at rows 4*ty.., columns 4*tx.., and for the 64 x 128 products the rows 4*ty.. and the columns
-// tx + 16*c (c = 0..7), which makes every shared-memory access of a warp conflict-free or a broadcast.
+// Both kernels use 64 x 64 score tiles and 256 threads laid out 16 x 16. Shared memory is the resource that
+// bounds a register-tiled FP32 product (one 128-byte wavefront per clock and SM against four FMA instructions per
+// clock), so every operand is fetched with 16-byte loads that are free of bank conflicts:
+//   scores (64 x 64, contraction over d):  thread (ty, tx) owns rows 4*ty+i and columns tx+16*j (i, j = 0..3) and
+//     reads four consecutive d of a row at a time; rows are 132 floats apart, and 132/4 = 33 is odd, so the pieces
+//     that eight neighbouring tx read from eight neighbouring rows fall into eight different bank groups;
+//   64 x 128 products (contraction over a tile edge):  thread (ty, tx) owns rows 4*ty+i and the eight columns
+//     4*tx+64*h+e (h = 0..1, e = 0..3): the 16 tx of a row read 256 contiguous bytes, the left operand is a broadcast.
+// P and dS tiles ([q][kv], row stride 68) are written with the score layout (conflict-free) and read back 16 bytes
+// at a time along either axis. Measured on the part: a 16-byte load costs one wavefront per quarter-warp (two when
+// a half-warp reads one address), i.e. 24 wavefronts per 64 FMA instructions in the score products and 40 per 128 in
+// the others -- the shared-memory pipe, not the FMA pipe, still sets the pace (FMA pipe 40-43 % busy); only a larger
+// register tile per thread would change that ratio.
 #include "lvx_internal.h"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -20,10 +30,24 @@
 namespace lvx {
 
 constexpr int SM_T = 64;            // tile edge
-constexpr int SM_LD = 129;          // padded row stride of a [64][128] tile
-constexpr int SM_LDP = 65;          // padded row stride of a [64][64] tile
+constexpr int SM_LD = 132;          // row stride of a [64][128] tile (floats): 16-byte aligned rows, 33 bank groups
+constexpr int SM_LDP = 68;          // row stride of a [64][64] tile
 constexpr int SM_TILE = SM_T * SM_LD;
 constexpr int SM_PTILE = SM_T * SM_LDP;
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float comp(const float4& v, int e) { return e == 0 ? v.x : e == 1 ? v.y : e == 2 ? v.z : v.w; }
+// acc[0..3] += s * v
+__device__ __forceinline__ void axpy4(float* acc, float s, const float4& v) {
+  acc[0] = fmaf(s, v.x, acc[0]);
+  acc[1] = fmaf(s, v.y, acc[1]);
+  acc[2] = fmaf(s, v.z, acc[2]);
+  acc[3] = fmaf(s, v.w, acc[3]);
+}
+// acc += a . b
+__device__ __forceinline__ float dot4(const float4& a, const float4& b, float acc) {
+  return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, acc))));
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
@@ -68,14 +92,14 @@ struct Fp32FwdParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 fp32_fwd_kernel(const Fp32FwdParams p) {
   if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* sQ = sm;
   float* sK = sQ + SM_TILE;
   float* sV = sK + SM_TILE;
-  float* sP = sV + SM_TILE;
+  float* sP = sK;                              // P takes K's place once the scores of a tile are in registers
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
   const int mb = blockIdx.x, slab = blockIdx.y, split = blockIdx.z;
   const int kvs = slab % p.kv_slabs;          // several query blocks may share one K/V batch entry
@@ -95,7 +119,7 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
   }
 
   load_tile(sQ, qs, mb * SM_T, p.rows, tid);
-  float m[4], l[4], o[4][8];
+  float m[4], l[4], o[4][8];                  // o[i][4*h+e]: row 4*ty+i, column 4*tx+64*h+e
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     m[i] = -INFINITY;
@@ -104,33 +128,35 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
     for (int c = 0; c < 8; ++c) o[i][c] = 0.f;
   }
   for (int kv0 = kv_begin; kv0 < kv_end; kv0 += SM_T) {
-    __syncthreads();
+    __syncthreads();                           // the previous tile's P and V have been consumed
     load_tile(sK, ks, kv0, p.skv, tid);
     load_tile(sV, vs, kv0, p.skv, tid);
     __syncthreads();
-    float s[4][4];
+    float s[4][4];                             // s[i][j]: row 4*ty+i, key tx+16*j
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
-    for (int d = 0; d < 128; ++d) {
-      float a[4], b[4];
+#pragma unroll 2
+    for (int d = 0; d < 128; d += 4) {
+      float4 a[4], b[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = sQ[(ty * 4 + i) * SM_LD + d];
+      for (int i = 0; i < 4; ++i) a[i] = ld4(sQ + (ty * 4 + i) * SM_LD + d);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = sK[(tx * 4 + j) * SM_LD + d];
+      for (int j = 0; j < 4; ++j) b[j] = ld4(sK + (tx + 16 * j) * SM_LD + d);
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) s[i][j] = fmaf(a[i], b[j], s[i][j]);
+        for (int j = 0; j < 4; ++j) s[i][j] = dot4(a[i], b[j], s[i][j]);
     }
+    __syncthreads();                           // every thread is done with K before P overwrites it
     // online softmax in base 2; a row is spread over the 16 threads that share ty
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float mx = -INFINITY;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int col = kv0 + tx * 4 + j;
+        const int col = kv0 + tx + 16 * j;
         float sc = -INFINITY;
         if (col < kv_end) {
           sc = s[i][j] * p.scale_log2;
@@ -149,7 +175,7 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
       for (int j = 0; j < 4; ++j) {
         const float pv = exp2f(s[i][j] - moff);
         sum += pv;
-        sP[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv;
+        sP[(ty * 4 + i) * SM_LDP + tx + 16 * j] = pv;
       }
 #pragma unroll
       for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
@@ -159,16 +185,21 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
       for (int c = 0; c < 8; ++c) o[i][c] *= alpha;
     }
     __syncthreads();
-    for (int j = 0; j < SM_T; ++j) {
-      float pr[4], vv[8];
+#pragma unroll 1
+    for (int j = 0; j < SM_T; j += 4) {
+      float4 pr[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) pr[i] = sP[(ty * 4 + i) * SM_LDP + j];
+      for (int i = 0; i < 4; ++i) pr[i] = ld4(sP + (ty * 4 + i) * SM_LDP + j);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) vv[c] = sV[j * SM_LD + tx + 16 * c];
+      for (int jj = 0; jj < 4; ++jj) {
+        const float4 v0 = ld4(sV + (j + jj) * SM_LD + 4 * tx);
+        const float4 v1 = ld4(sV + (j + jj) * SM_LD + 64 + 4 * tx);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) o[i][c] = fmaf(pr[i], vv[c], o[i][c]);
+        for (int i = 0; i < 4; ++i) {
+          axpy4(&o[i][0], comp(pr[i], jj), v0);
+          axpy4(&o[i][4], comp(pr[i], jj), v1);
+        }
+      }
     }
   }
 #pragma unroll
@@ -177,7 +208,9 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
     if (row >= p.rows) continue;
     const size_t prow = (size_t(slab) * p.nsplit + split) * p.rows + row;
 #pragma unroll
-    for (int c = 0; c < 8; ++c) p.o_part[prow * 128 + tx + 16 * c] = o[i][c];
+    for (int h = 0; h < 2; ++h)
+      *reinterpret_cast<float4*>(p.o_part + prow * 128 + 64 * h + 4 * tx) =
+          make_float4(o[i][4 * h], o[i][4 * h + 1], o[i][4 * h + 2], o[i][4 * h + 3]);
     if (tx == 0) {
       p.ml_part[prow * 2] = m[i];
       p.ml_part[prow * 2 + 1] = l[i];
@@ -199,10 +232,10 @@ struct Fp32BwdParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 fp32_bwd_kernel(const Fp32BwdParams p) {
   if (p.status && *reinterpret_cast<const volatile int*>(p.status) != 0) return;
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* sK = sm;
   float* sV = sK + SM_TILE;
   float* sQ = sV + SM_TILE;
@@ -217,7 +250,7 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
 
   load_tile(sK, static_cast<const T*>(p.k) + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
   load_tile(sV, static_cast<const T*>(p.v) + size_t(slab) * p.skv * 128, kv0, p.skv, tid);
-  float dk[4][8], dv[4][8];
+  float dk[4][8], dv[4][8];      // [i][4*h+e]: key row 4*ty+i, column 4*tx+64*h+e
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -237,97 +270,100 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
     load_tile(sQ, qs, q0, p.rows, tid);
     load_tile(sDO, dos, q0, p.rows, tid);
     __syncthreads();
-    float s[4][4], dp[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) s[i][j] = dp[i][j] = 0.f;
-    for (int d = 0; d < 128; ++d) {
-      float a[4], g[4], b[4], w[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        a[i] = sQ[(ty * 4 + i) * SM_LD + d];
-        g[i] = sDO[(ty * 4 + i) * SM_LD + d];
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        b[j] = sK[(tx * 4 + j) * SM_LD + d];
-        w[j] = sV[(tx * 4 + j) * SM_LD + d];
-      }
+    {
+      // S[q][kv] = Q K^T and dP[q][kv] = dO V^T    (this thread: q rows 4*ty+i, keys tx+16*j)
+      float s[4][4], dp[4][4];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          s[i][j] = fmaf(a[i], b[j], s[i][j]);
-          dp[i][j] = fmaf(g[i], w[j], dp[i][j]);
-        }
-    }
+        for (int j = 0; j < 4; ++j) s[i][j] = dp[i][j] = 0.f;
+#pragma unroll 1
+      for (int d = 0; d < 128; d += 4) {
+        float4 a[4], b[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int qrow = q0 + ty * 4 + i;
-      float l2 = INFINITY, dl = 0.f;      // +inf: rows that do not exist, or that have no valid key anywhere
-      if (qrow < p.rows) {
-        l2 = lses[qrow] * 1.4426950408889634f;
-        if (l2 == -INFINITY) l2 = INFINITY;
-        dl = deltas[qrow];
+        for (int i = 0; i < 4; ++i) a[i] = ld4(sQ + (ty * 4 + i) * SM_LD + d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = ld4(sK + (tx + 16 * j) * SM_LD + d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) s[i][j] = dot4(a[i], b[j], s[i][j]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a[i] = ld4(sDO + (ty * 4 + i) * SM_LD + d);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) b[j] = ld4(sV + (tx + 16 * j) * SM_LD + d);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) dp[i][j] = dot4(a[i], b[j], dp[i][j]);
       }
-      const float* br = qrow < p.rows ? bias_row(p.bias, qslab, slab, p.kv_slabs, p.hkv, qrow) : nullptr;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int col = kv0 + tx * 4 + j;
-        const bool ok = col < valid;
-        float sc = s[i][j] * p.scale_log2;
-        if (ok && br) sc = fmaf(br[col * p.bias.s_kv], 1.4426950408889634f, sc);
-        const float pv = ok ? exp2f(sc - l2) : 0.f;
-        sP[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv;
-        sDS[(ty * 4 + i) * SM_LDP + tx * 4 + j] = pv * (dp[i][j] - dl);
+      for (int i = 0; i < 4; ++i) {
+        const int qrow = q0 + ty * 4 + i;
+        float l2 = INFINITY, dl = 0.f;      // +inf: rows that do not exist, or that have no valid key anywhere
+        if (qrow < p.rows) {
+          l2 = lses[qrow] * 1.4426950408889634f;
+          if (l2 == -INFINITY) l2 = INFINITY;
+          dl = deltas[qrow];
+        }
+        const float* br = qrow < p.rows ? bias_row(p.bias, qslab, slab, p.kv_slabs, p.hkv, qrow) : nullptr;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int col = kv0 + tx + 16 * j;
+          const bool ok = col < valid;
+          float sc = s[i][j] * p.scale_log2;
+          if (ok && br) sc = fmaf(br[col * p.bias.s_kv], 1.4426950408889634f, sc);
+          const float pv = ok ? exp2f(sc - l2) : 0.f;
+          sP[(ty * 4 + i) * SM_LDP + tx + 16 * j] = pv;
+          sDS[(ty * 4 + i) * SM_LDP + tx + 16 * j] = pv * (dp[i][j] - dl);
+        }
       }
     }
     __syncthreads();
-    // dV[kv][d] += sum_q P[q][kv] dO[q][d];  dK[kv][d] += sum_q dS[q][kv] Q[q][d]   (this thread: kv rows 4*ty.., d = tx+16c)
+    // dV[kv][d] += sum_q P[q][kv] dO[q][d];  dK[kv][d] += sum_q dS[q][kv] Q[q][d]
+    // (this thread: key rows 4*ty+i -- one 16-byte piece of a P / dS row -- and columns 4*tx+64*h+e)
+#pragma unroll 2
     for (int qi = 0; qi < SM_T; ++qi) {
-      float pr[4], dsr[4], g[8], a[8];
+      const float4 pr = ld4(sP + qi * SM_LDP + 4 * ty);
+      const float4 dsr = ld4(sDS + qi * SM_LDP + 4 * ty);
+      const float4 g0 = ld4(sDO + qi * SM_LD + 4 * tx), g1 = ld4(sDO + qi * SM_LD + 64 + 4 * tx);
+      const float4 a0 = ld4(sQ + qi * SM_LD + 4 * tx), a1 = ld4(sQ + qi * SM_LD + 64 + 4 * tx);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        pr[i] = sP[qi * SM_LDP + ty * 4 + i];
-        dsr[i] = sDS[qi * SM_LDP + ty * 4 + i];
+        axpy4(&dv[i][0], comp(pr, i), g0);
+        axpy4(&dv[i][4], comp(pr, i), g1);
+        axpy4(&dk[i][0], comp(dsr, i), a0);
+        axpy4(&dk[i][4], comp(dsr, i), a1);
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        g[c] = sDO[qi * SM_LD + tx + 16 * c];
-        a[c] = sQ[qi * SM_LD + tx + 16 * c];
-      }
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          dv[i][c] = fmaf(pr[i], g[c], dv[i][c]);
-          dk[i][c] = fmaf(dsr[i], a[c], dk[i][c]);
-        }
     }
-    // dQ[q][d] = sum_kv dS[q][kv] K[kv][d]    (this thread: q rows 4*ty.., d = tx+16c)
+    // dQ[q][d] = sum_kv dS[q][kv] K[kv][d]    (this thread: q rows 4*ty+i, columns 4*tx+64*h+e)
     float dq[4][8];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int c = 0; c < 8; ++c) dq[i][c] = 0.f;
-    for (int j = 0; j < SM_T; ++j) {
-      float dsr[4], b[8];
+#pragma unroll 1
+    for (int j = 0; j < SM_T; j += 4) {
+      float4 dsr[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) dsr[i] = sDS[(ty * 4 + i) * SM_LDP + j];
+      for (int i = 0; i < 4; ++i) dsr[i] = ld4(sDS + (ty * 4 + i) * SM_LDP + j);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) b[c] = sK[j * SM_LD + tx + 16 * c];
+      for (int jj = 0; jj < 4; ++jj) {
+        const float4 b0 = ld4(sK + (j + jj) * SM_LD + 4 * tx), b1 = ld4(sK + (j + jj) * SM_LD + 64 + 4 * tx);
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int c = 0; c < 8; ++c) dq[i][c] = fmaf(dsr[i], b[c], dq[i][c]);
+        for (int i = 0; i < 4; ++i) {
+          axpy4(&dq[i][0], comp(dsr[i], jj), b0);
+          axpy4(&dq[i][4], comp(dsr[i], jj), b1);
+        }
+      }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int qrow = q0 + ty * 4 + i;
       if (qrow < p.rows)
 #pragma unroll
-        for (int c = 0; c < 8; ++c) atomicAdd(dqs + size_t(qrow) * 128 + tx + 16 * c, dq[i][c] * p.scale);
+        for (int c = 0; c < 8; ++c)
+          atomicAdd(dqs + size_t(qrow) * 128 + 64 * (c >> 2) + 4 * tx + (c & 3), dq[i][c] * p.scale);
     }
   }
 #pragma unroll
@@ -338,7 +374,7 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
     const size_t off = (size_t(slab) * p.skv + row) * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c) {
-      const int d = tx + 16 * c;
+      const int d = 64 * (c >> 2) + 4 * tx + (c & 3);
       const float a = dk[i][c] * p.scale, b = dv[i][c];
       if (p.accumulate == 2) {                          // finished gradients in the input dtype
         from_f32(static_cast<T*>(p.dk_acc) + off + d, a);
@@ -385,7 +421,7 @@ int launch_fwd_block_simt(const lvx_shape& s, const FwdPlan& pl, const void* q, 
   p.o_part = o_part;
   p.ml_part = ml_part;
   p.status = device_status_ptr();
-  const int smem = (3 * SM_TILE + SM_PTILE) * sizeof(float);
+  const int smem = 3 * SM_TILE * sizeof(float);   // P shares K's tile
   dim3 grid((pl.rows + SM_T - 1) / SM_T, q_blocks_of(s) * s.B * s.Hkv, pl.nsplit);
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern) {

@@ -1,7 +1,11 @@
 // Backward flash-attention block for sm_100a.
 //
-// A CTA owns one 128-row K/V tile of one (batch, kv head) and walks over the packed query rows of the
-// group (g*Sq rows of every query block, 128 at a time). Everything is computed in the transposed frame, so
+// A work item is one 128-row K/V tile of one (batch, kv head); a CTA walks over the packed query rows of the
+// group for it (g*Sq rows of every query block, 128 at a time). The grid is persistent -- one CTA per SM, items
+// handed out round-robin -- so that the fixed costs of an item (launch, barrier and TMEM set-up, the K/V load, the
+// dK/dV write-out and the last dQ^T drain, about 8 us against 3.3 us per query tile) overlap with the next item's
+// start instead of standing between two CTAs: all barrier phases simply keep counting tiles and items across the
+// items of a CTA. Everything is computed in the transposed frame, so
 // that the softmax statistics are per column and no row reduction is needed:
 //     S^T  = K Q^T            (smem x smem)       P^T  = exp2(S^T*c - lse[col])
 //     dP^T = V dO^T           (smem x smem)       dS^T = P^T o (dP^T - delta[col])
@@ -43,6 +47,7 @@
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <algorithm>
 
 namespace lvx {
 
@@ -89,6 +94,8 @@ struct BwdParams {
   int hkv;
   int nblk;            // query blocks per K/V batch entry (query slab = kv slab + block * kv_slabs)
   int kv_slabs;        // B*Hkv
+  int kv_tiles;        // 128-row K/V tiles per slab
+  int nitems;          // kv_tiles * kv_slabs work items, item w = (tile w % kv_tiles, slab w / kv_tiles)
   const int32_t* kv_valid_len;
   const float* lse;    // [nblk*B*Hq*Sq]  == [query slab][rows]
   const float* delta;
@@ -134,16 +141,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   float* s_stat = reinterpret_cast<float*>(smem + BWD_OFF_STAT);   // [2][256]: lse*log2(e) then delta
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kv_tile = blockIdx.x, slab = blockIdx.y;
-  const int batch = slab / p.hkv;
-  const int kv0 = kv_tile * 128;
-
-  int valid = p.skv;
-  if (p.kv_valid_len) valid = min(valid, max(0, p.kv_valid_len[batch]));
-  const bool tile_live = kv0 < valid;          // at least one valid K/V row in this tile
-  const bool tile_partial = valid < kv0 + 128; // some rows of the tile are padding
+  struct Item {
+    int slab, kv0, valid;
+    bool live, partial;      // at least one valid K/V row in the tile; some rows of the tile are padding
+  };
+  auto item_of = [&](int w) {
+    Item it;
+    it.slab = w / p.kv_tiles;
+    it.kv0 = (w % p.kv_tiles) * 128;
+    it.valid = p.skv;
+    if (p.kv_valid_len) it.valid = min(it.valid, max(0, p.kv_valid_len[it.slab / p.hkv]));
+    it.live = it.kv0 < it.valid;
+    it.partial = it.valid < it.kv0 + 128;
+    return it;
+  };
   const int nq = (p.rows + 127) >> 7;         // 128-row tiles per query block
-  const int ntot = nq * p.nblk;               // tiles this CTA walks: all blocks, one after the other
+  const int ntot = nq * p.nblk;               // tiles walked per item: all blocks, one after the other
   // The operand descriptors assume 1024-byte aligned tiles; refuse to run otherwise.
   const bool misaligned = (smem_u32(smem) & 1023u) != 0;
   if (misaligned && tid == 0) atomicCAS(p.status, 0, BWD_CODE(7, 0));
@@ -178,180 +191,209 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (!poisoned && tile_live) {
+  // Every role walks the same items in the same order and keeps the same two counters: `it` = live items done,
+  // `jj0` = query tiles done before the current item. Barriers that complete once per tile take their phase from
+  // jj = jj0 + j, those that complete once per item (KV_FULL, ACC_DONE) from `it`.
+  if (!poisoned) {
     if (warp < BWD_COMPUTE_WARPS) {
       // =========================== compute warps ===========================
       const int quarter = warp & 3;                         // TMEM lane quarter
       const int cg = warp >> 2;                             // 32-column group of the query tile
       const int r = quarter * 32 + lane;                    // K/V row inside the tile (head-dim index in the drain)
-      const bool row_valid = (kv0 + r) < valid;
       const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
       const uint32_t tX = tmem_base + TM_X + lane_sel, tY = tmem_base + TM_Y + lane_sel;
       const float c = p.scale_log2;
-      // tile j -> (query slab, first row inside the block); blocks are walked starting with this rank's own
-      auto tile_slab = [&](int j) { return slab + ((p.bw.first_blk + j / nq) % p.nblk) * p.kv_slabs; };
-      auto tile_row0 = [&](int j) { return (j % nq) * 128; };
-      // Per-column statistics of a query tile: threads 0-127 fetch lse, 128-255 delta (warps 0-7).
-      auto fetch_stat = [&](int j) -> float {
-        // the first tile of a block that another rank sends: its statistics must have landed
-        if (tid < 256 && (j % nq) == 0 && !wait_block(p.bw, (p.bw.first_blk + j / nq) % p.nblk, abort_flag, p.status))
-          return 0.f;
-        const int qrow = tile_row0(j) + (tid & 127);
-        const size_t stat_base = size_t(tile_slab(j)) * p.rows;
-        if (tid < 128) {
-          float v = INFINITY;   // +inf => P = 0 for query rows that do not exist
-          if (qrow < p.rows) {
-            v = p.lse[stat_base + qrow] * 1.4426950408889634f;
-            if (v == -INFINITY) v = INFINITY;   // a row with no valid key anywhere has P = 0
-          }
-          return v;
-        }
-        return (tid < 256 && qrow < p.rows) ? p.delta[stat_base + qrow] : 0.f;
-      };
-      // Two buffers are enough: a warp publishes tile j+1 only after the XY_LOADED rendezvous of tile j,
-      // which every warp reaches after it has finished reading the statistics of tile j-1.
-      auto put_stat = [&](int j, float v) {
-        if (tid >= 256) return;
-        s_stat[(j & 1) * 256 + tid] = v;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_STAT_FULL + (j & 1)]);
-      };
-      put_stat(0, fetch_stat(0));
-      float stat_next = ntot > 1 ? fetch_stat(1) : 0.f;   // fetched two tiles ahead, published one ahead
       bool alive = true;
-      for (int j = 0; j < ntot; ++j) {
-        float stat_after = 0.f;
-        if (j + 2 < ntot) stat_after = fetch_stat(j + 2);
-        if (warp == 0) BWD_TS(0, 0);
-        // ---------------- P^T half: needs S^T only ----------------
-        if (!mbar_wait(&bars[BB_S_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL), p.bw.pipe_limit)) {
-          alive = false;
-          break;
-        }
-        tc_fence_after();
-        if (warp == 0) BWD_TS(0, 1);
-        uint32_t s[32];
-        tmem_ld32(tX + cg * 32, s);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_X_LOADED]);
-        if (!mbar_wait(&bars[BB_STAT_FULL + (j & 1)], (j >> 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_STAT_FULL), p.bw.pipe_limit)) {
-          alive = false;
-          break;
-        }
-        const float4* sl = reinterpret_cast<const float4*>(s_stat + (j & 1) * 256 + cg * 32);
-        const float4* sd = reinterpret_cast<const float4*>(s_stat + (j & 1) * 256 + 128 + cg * 32);
-        uint32_t pk[16];
+      int it = 0, jj0 = 0;
+      for (int w = blockIdx.x; alive && w < p.nitems; w += gridDim.x) {
+        const Item I = item_of(w);
+        if (!I.live) {
+          // No valid K/V row in this tile: its gradients are zero.
+          if (p.accumulate != 1 && warp < 8 && I.kv0 + (tid & 127) < p.skv) {
+            const size_t off = (size_t(I.slab) * p.skv + I.kv0 + (tid & 127)) * 128;
+            float* base = warp < 4 ? p.dk_acc : p.dv_acc;
+            if (p.accumulate == 2) {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + off);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 l2 = sl[i];
-          float p0 = ex2f(fmaf(__uint_as_float(s[4 * i]), c, -l2.x));
-          float p1 = ex2f(fmaf(__uint_as_float(s[4 * i + 1]), c, -l2.y));
-          float p2 = ex2f(fmaf(__uint_as_float(s[4 * i + 2]), c, -l2.z));
-          float p3 = ex2f(fmaf(__uint_as_float(s[4 * i + 3]), c, -l2.w));
-          if (tile_partial && !row_valid) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
-          pk[2 * i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-          pk[2 * i + 1] = IS_BF16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
-        }
-        if (warp == 0) BWD_TS(0, 2);
-        // P^T overwrites S^T in X: wait until every warp has taken its S^T columns out.
-        if (!mbar_wait(&bars[BB_X_LOADED], j & 1, abort_flag, p.status, BWD_CODE(0, BB_X_LOADED), p.bw.pipe_limit)) {
-          alive = false;
-          break;
-        }
-        tmem_st16(tX + cg * 16, pk);
-        tc_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_P_FULL]);      // dV of this tile may start
-        // ---------------- dS^T half: needs dP^T ----------------
-        if (!mbar_wait(&bars[BB_DP_FULL], j & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL), p.bw.pipe_limit)) {
-          alive = false;
-          break;
-        }
-        tc_fence_after();
-        if (warp == 0) BWD_TS(0, 3);
-        uint32_t dsk[16];
+              for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+            } else {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t dp[16];
-          tmem_ld16(tY + cg * 32 + h * 16, dp);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            // P is taken back from its packed 16-bit form (the value the dV product uses), which keeps only
-            // 16 registers alive across the wait for dP^T
-            const float4 dl = sd[h * 4 + i];
-            const float2 pa = unpack16x2<IS_BF16>(pk[h * 8 + 2 * i]), pb = unpack16x2<IS_BF16>(pk[h * 8 + 2 * i + 1]);
-            const float d0 = pa.x * (__uint_as_float(dp[4 * i]) - dl.x);
-            const float d1 = pa.y * (__uint_as_float(dp[4 * i + 1]) - dl.y);
-            const float d2 = pb.x * (__uint_as_float(dp[4 * i + 2]) - dl.z);
-            const float d3 = pb.y * (__uint_as_float(dp[4 * i + 3]) - dl.w);
-            dsk[h * 8 + 2 * i] = IS_BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
-            dsk[h * 8 + 2 * i + 1] = IS_BF16 ? pack_bf16x2(d2, d3) : pack_f16x2(d2, d3);
+              for (int i = 0; i < 32; ++i) reinterpret_cast<float4*>(base + off)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
           }
+          continue;
         }
-        tc_fence_before();
-        // dS^T row -> shared memory: two 64-column halves, each 128-byte swizzled (chunk ^ row%8). The
-        // previous tile's dQ^T and dK products must have finished reading the buffer.
-        if (j > 0 && !mbar_wait(&bars[BB_DS_FREE], (j - 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_DS_FREE), p.bw.pipe_limit)) {
-          alive = false;
-          break;
-        }
-        {
-          uint8_t* rowp = smem + BWD_OFF_DS + (cg >> 1) * BWD_HALF + r * 128;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint4 v = make_uint4(dsk[4 * ch], dsk[4 * ch + 1], dsk[4 * ch + 2], dsk[4 * ch + 3]);
-            *reinterpret_cast<uint4*>(rowp + ((((cg & 1) * 4 + ch) ^ (r & 7)) << 4)) = v;
+        const bool row_valid = (I.kv0 + r) < I.valid;
+        // tile j -> (query slab, first row inside the block); blocks are walked starting with this rank's own
+        auto tile_slab = [&](int j) { return I.slab + ((p.bw.first_blk + j / nq) % p.nblk) * p.kv_slabs; };
+        auto tile_row0 = [&](int j) { return (j % nq) * 128; };
+        // Per-column statistics of a query tile: threads 0-127 fetch lse, 128-255 delta (warps 0-7).
+        auto fetch_stat = [&](int j) -> float {
+          // the first tile of a block that another rank sends: its statistics must have landed
+          if (tid < 256 && (j % nq) == 0 && !wait_block(p.bw, (p.bw.first_blk + j / nq) % p.nblk, abort_flag, p.status))
+            return 0.f;
+          const int qrow = tile_row0(j) + (tid & 127);
+          const size_t stat_base = size_t(tile_slab(j)) * p.rows;
+          if (tid < 128) {
+            float v = INFINITY;   // +inf => P = 0 for query rows that do not exist
+            if (qrow < p.rows) {
+              v = p.lse[stat_base + qrow] * 1.4426950408889634f;
+              if (v == -INFINITY) v = INFINITY;   // a row with no valid key anywhere has P = 0
+            }
+            return v;
           }
-        }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_PDS_FULL]);
-        if (warp == 0) BWD_TS(0, 4);
-        if (j + 1 < ntot) put_stat(j + 1, stat_next);
-        stat_next = stat_after;
-      }
-      // ------------------------------- dK / dV epilogue -------------------------------
-      if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], 0, abort_flag, p.status, BWD_CODE(0, BB_ACC_DONE), p.bw.pipe_limit);
-      tc_fence_after();
-      if (alive) {
-        const bool ok_row = (kv0 + r) < p.skv;
-        const size_t off = (size_t(slab) * p.skv + kv0 + r) * 128 + cg * 32;
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          uint32_t a[32];
-          tmem_ld32(tmem_base + (which ? TM_DV : TM_DK) + lane_sel + cg * 32, a);
+          return (tid < 256 && qrow < p.rows) ? p.delta[stat_base + qrow] : 0.f;
+        };
+        // Two buffers are enough: a warp publishes tile jj+1 only after the X_LOADED rendezvous of tile jj,
+        // which every warp reaches after it has finished reading the statistics of tile jj-1 (also across items).
+        auto put_stat = [&](int jj, float v) {
+          if (tid >= 256) return;
+          s_stat[(jj & 1) * 256 + tid] = v;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[BB_STAT_FULL + (jj & 1)]);
+        };
+        put_stat(jj0, fetch_stat(0));
+        float stat_next = ntot > 1 ? fetch_stat(1) : 0.f;   // fetched two tiles ahead, published one ahead
+        for (int j = 0; j < ntot; ++j) {
+          const int jj = jj0 + j;
+          float stat_after = 0.f;
+          if (j + 2 < ntot) stat_after = fetch_stat(j + 2);
+          if (warp == 0) BWD_TS(0, 0);
+          // ---------------- P^T half: needs S^T only ----------------
+          if (!mbar_wait(&bars[BB_S_FULL], jj & 1, abort_flag, p.status, BWD_CODE(0, BB_S_FULL), p.bw.pipe_limit)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          if (warp == 0) BWD_TS(0, 1);
+          uint32_t s[32];
+          tmem_ld32(tX + cg * 32, s);
           tc_wait_ld();
-          const float mul = which ? 1.f : p.scale;
-          if (ok_row && p.accumulate == 2) {
-            uint4* d16 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(which ? p.dv_acc : p.dk_acc) + off);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[BB_X_LOADED]);
+          if (!mbar_wait(&bars[BB_STAT_FULL + (jj & 1)], (jj >> 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_STAT_FULL), p.bw.pipe_limit)) {
+            alive = false;
+            break;
+          }
+          const float4* sl = reinterpret_cast<const float4*>(s_stat + (jj & 1) * 256 + cg * 32);
+          const float4* sd = reinterpret_cast<const float4*>(s_stat + (jj & 1) * 256 + 128 + cg * 32);
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 l2 = sl[i];
+            float p0 = ex2f(fmaf(__uint_as_float(s[4 * i]), c, -l2.x));
+            float p1 = ex2f(fmaf(__uint_as_float(s[4 * i + 1]), c, -l2.y));
+            float p2 = ex2f(fmaf(__uint_as_float(s[4 * i + 2]), c, -l2.z));
+            float p3 = ex2f(fmaf(__uint_as_float(s[4 * i + 3]), c, -l2.w));
+            if (I.partial && !row_valid) { p0 = 0.f; p1 = 0.f; p2 = 0.f; p3 = 0.f; }
+            pk[2 * i] = IS_BF16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
+            pk[2 * i + 1] = IS_BF16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
+          }
+          if (warp == 0) BWD_TS(0, 2);
+          // P^T overwrites S^T in X: wait until every warp has taken its S^T columns out.
+          if (!mbar_wait(&bars[BB_X_LOADED], jj & 1, abort_flag, p.status, BWD_CODE(0, BB_X_LOADED), p.bw.pipe_limit)) {
+            alive = false;
+            break;
+          }
+          tmem_st16(tX + cg * 16, pk);
+          tc_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[BB_P_FULL]);      // dV of this tile may start
+          // ---------------- dS^T half: needs dP^T ----------------
+          if (!mbar_wait(&bars[BB_DP_FULL], jj & 1, abort_flag, p.status, BWD_CODE(0, BB_DP_FULL), p.bw.pipe_limit)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          if (warp == 0) BWD_TS(0, 3);
+          uint32_t dsk[16];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t dp[16];
+            tmem_ld16(tY + cg * 32 + h * 16, dp);
+            tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              uint32_t w[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float lo = __uint_as_float(a[8 * i + 2 * e]) * mul, hi = __uint_as_float(a[8 * i + 2 * e + 1]) * mul;
-                w[e] = IS_BF16 ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
-              }
-              d16[i] = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-          } else if (ok_row) {
-            float4* d4 = reinterpret_cast<float4*>((which ? p.dv_acc : p.dk_acc) + off);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float4 v = make_float4(__uint_as_float(a[4 * i]) * mul, __uint_as_float(a[4 * i + 1]) * mul,
-                                     __uint_as_float(a[4 * i + 2]) * mul, __uint_as_float(a[4 * i + 3]) * mul);
-              if (p.accumulate == 1) {
-                const float4 o = d4[i];
-                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-              }
-              d4[i] = v;
+              // P is taken back from its packed 16-bit form (the value the dV product uses), which keeps only
+              // 16 registers alive across the wait for dP^T
+              const float4 dl = sd[h * 4 + i];
+              const float2 pa = unpack16x2<IS_BF16>(pk[h * 8 + 2 * i]), pb = unpack16x2<IS_BF16>(pk[h * 8 + 2 * i + 1]);
+              const float d0 = pa.x * (__uint_as_float(dp[4 * i]) - dl.x);
+              const float d1 = pa.y * (__uint_as_float(dp[4 * i + 1]) - dl.y);
+              const float d2 = pb.x * (__uint_as_float(dp[4 * i + 2]) - dl.z);
+              const float d3 = pb.y * (__uint_as_float(dp[4 * i + 3]) - dl.w);
+              dsk[h * 8 + 2 * i] = IS_BF16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
+              dsk[h * 8 + 2 * i + 1] = IS_BF16 ? pack_bf16x2(d2, d3) : pack_f16x2(d2, d3);
             }
           }
+          tc_fence_before();
+          // dS^T row -> shared memory: two 64-column halves, each 128-byte swizzled (chunk ^ row%8). The
+          // previous tile's dQ^T and dK products (of this item or the one before) must have finished reading it.
+          if (jj > 0 && !mbar_wait(&bars[BB_DS_FREE], (jj - 1) & 1, abort_flag, p.status, BWD_CODE(0, BB_DS_FREE), p.bw.pipe_limit)) {
+            alive = false;
+            break;
+          }
+          {
+            uint8_t* rowp = smem + BWD_OFF_DS + (cg >> 1) * BWD_HALF + r * 128;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint4 v = make_uint4(dsk[4 * ch], dsk[4 * ch + 1], dsk[4 * ch + 2], dsk[4 * ch + 3]);
+              *reinterpret_cast<uint4*>(rowp + ((((cg & 1) * 4 + ch) ^ (r & 7)) << 4)) = v;
+            }
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[BB_PDS_FULL]);
+          if (warp == 0) BWD_TS(0, 4);
+          if (j + 1 < ntot) put_stat(jj + 1, stat_next);
+          stat_next = stat_after;
         }
+        // ------------------------------- dK / dV of the item -------------------------------
+        // The issuer is already on the next item's S^T / dP^T (X and Y); it overwrites dK / dV only after every
+        // compute warp has published the next item's first P^T, i.e. after these loads.
+        if (alive) alive = mbar_wait(&bars[BB_ACC_DONE], it & 1, abort_flag, p.status, BWD_CODE(0, BB_ACC_DONE), p.bw.pipe_limit);
+        tc_fence_after();
+        if (alive) {
+          const bool ok_row = (I.kv0 + r) < p.skv;
+          const size_t off = (size_t(I.slab) * p.skv + I.kv0 + r) * 128 + cg * 32;
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            uint32_t a[32];
+            tmem_ld32(tmem_base + (which ? TM_DV : TM_DK) + lane_sel + cg * 32, a);
+            tc_wait_ld();
+            const float mul = which ? 1.f : p.scale;
+            if (ok_row && p.accumulate == 2) {
+              uint4* d16 = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(which ? p.dv_acc : p.dk_acc) + off);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint32_t wd[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float lo = __uint_as_float(a[8 * i + 2 * e]) * mul, hi = __uint_as_float(a[8 * i + 2 * e + 1]) * mul;
+                  wd[e] = IS_BF16 ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi);
+                }
+                d16[i] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+              }
+            } else if (ok_row) {
+              float4* d4 = reinterpret_cast<float4*>((which ? p.dv_acc : p.dk_acc) + off);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 v = make_float4(__uint_as_float(a[4 * i]) * mul, __uint_as_float(a[4 * i + 1]) * mul,
+                                       __uint_as_float(a[4 * i + 2]) * mul, __uint_as_float(a[4 * i + 3]) * mul);
+                if (p.accumulate == 1) {
+                  const float4 o = d4[i];
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                d4[i] = v;
+              }
+            }
+          }
+          tc_fence_before();
+        }
+        ++it;
+        jj0 += ntot;
       }
     } else if (warp < BWD_WARP_TMA) {
       // =========================== dQ drain warps ===========================
@@ -359,27 +401,38 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
       const int ch = (warp - BWD_COMPUTE_WARPS) >> 2;      // which 64 query columns
       const int d = quarter * 32 + lane;                    // head-dim index = TMEM lane of dQ^T
       const uint32_t tY = tmem_base + TM_Y + (static_cast<uint32_t>(quarter * 32) << 16) + ch * 64;
-      for (int j = 0; j < ntot; ++j) {
-        if (!mbar_wait(&bars[BB_DQ_FULL], j & 1, abort_flag, p.status, BWD_CODE(1, BB_DQ_FULL), p.bw.pipe_limit)) break;
-        tc_fence_after();
-        if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 5);
-        uint32_t v[2][32];
-        tmem_ld32(tY, v[0]);
-        tmem_ld32(tY + 32, v[1]);
-        tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);     // Y is free for the next tile's dP^T
-        if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 6);
-        {
-          const int row0 = (j % nq) * 128 + ch * 64;
-          const int ncols = min(64, p.rows - row0);
-          float* dst = p.dq_acc + (size_t(slab + ((p.bw.first_blk + j / nq) % p.nblk) * p.kv_slabs) * p.rows + row0) * 128 + d;
+      bool alive = true;
+      int jj0 = 0;
+      for (int w = blockIdx.x; alive && w < p.nitems; w += gridDim.x) {
+        const Item I = item_of(w);
+        if (!I.live) continue;
+        for (int j = 0; j < ntot; ++j) {
+          const int jj = jj0 + j;
+          if (!mbar_wait(&bars[BB_DQ_FULL], jj & 1, abort_flag, p.status, BWD_CODE(1, BB_DQ_FULL), p.bw.pipe_limit)) {
+            alive = false;
+            break;
+          }
+          tc_fence_after();
+          if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 5);
+          uint32_t v[2][32];
+          tmem_ld32(tY, v[0]);
+          tmem_ld32(tY + 32, v[1]);
+          tc_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[BB_DQ_FREE]);     // Y is free for the next tile's dP^T
+          if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 6);
+          {
+            const int row0 = (j % nq) * 128 + ch * 64;
+            const int ncols = min(64, p.rows - row0);
+            float* dst = p.dq_acc + (size_t(I.slab + ((p.bw.first_blk + j / nq) % p.nblk) * p.kv_slabs) * p.rows + row0) * 128 + d;
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (i < ncols) atomicAdd(dst + size_t(i) * 128, __uint_as_float(v[i >> 5][i & 31]) * p.scale);
+            for (int i = 0; i < 64; ++i)
+              if (i < ncols) atomicAdd(dst + size_t(i) * 128, __uint_as_float(v[i >> 5][i & 31]) * p.scale);
+          }
+          if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 7);
         }
-        if (warp == BWD_COMPUTE_WARPS) BWD_TS(0, 7);
+        jj0 += ntot;
       }
     } else if (warp == BWD_WARP_TMA) {
       // =========================== TMA producer ===========================
@@ -388,37 +441,58 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         tma_prefetch_desc(&tmDO);
         tma_prefetch_desc(&tmK);
         tma_prefetch_desc(&tmV);
-        mbar_arrive_expect_tx(&bars[BB_KV_FULL], 2 * BWD_TILE);
-        for (int h = 0; h < 2; ++h) {
-          tma_load_3d(smem + BWD_OFF_K + h * BWD_HALF, &tmK, &bars[BB_KV_FULL], h * 64, kv0, slab);
-          tma_load_3d(smem + BWD_OFF_V + h * BWD_HALF, &tmV, &bars[BB_KV_FULL], h * 64, kv0, slab);
-        }
-        int issued = 0;
-        for (int j = 0; j < ntot; ++j) {
-          const int s = j % BWD_NSQ;
-          const uint32_t ph = (j / BWD_NSQ) & 1;
-          const int blk = (p.bw.first_blk + j / nq) % p.nblk;
-          const int qslab = slab + blk * p.kv_slabs, y = (j % nq) * 128;
-          if (y == 0) {      // first tile of a block: it may still be on its way from another rank
-            if (!wait_block(p.bw, blk, abort_flag, p.status)) break;
-            fence_async_global();
+        int issued = 0, kv_loads = 0;        // Q/dO tiles and K/V tiles requested so far
+        bool alive = true;
+        int it = 0, jj0 = 0;
+        for (int w = blockIdx.x; alive && w < p.nitems; w += gridDim.x) {
+          const Item I = item_of(w);
+          if (!I.live) continue;
+          for (int j = 0; j < ntot; ++j) {
+            const int jj = jj0 + j;
+            const int s = jj % BWD_NSQ;
+            const uint32_t ph = (jj / BWD_NSQ) & 1;
+            const int blk = (p.bw.first_blk + j / nq) % p.nblk;
+            const int qslab = I.slab + blk * p.kv_slabs, y = (j % nq) * 128;
+            if (y == 0) {      // first tile of a block: it may still be on its way from another rank
+              if (!wait_block(p.bw, blk, abort_flag, p.status)) { alive = false; break; }
+              fence_async_global();
+            }
+            if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY), p.bw.pipe_limit)) {
+              alive = false;
+              break;
+            }
+            uint8_t* dstq = smem + BWD_OFF_Q + s * 2 * BWD_TILE;
+            mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_TILE);
+            for (int h = 0; h < 2; ++h) {
+              tma_load_3d(dstq + h * BWD_HALF, &tmQ, &bars[BB_Q_FULL + s], h * 64, y, qslab);
+              tma_load_3d(dstq + BWD_TILE + h * BWD_HALF, &tmDO, &bars[BB_Q_FULL + s], h * 64, y, qslab);
+            }
+            issued = jj + 1;
+            if (j == 0) {
+              // The item's K/V go in after its first Q/dO tile (whose stage frees early): the tile buffers are
+              // the previous item's until all of its products have completed.
+              if (it > 0 && !mbar_wait(&bars[BB_ACC_DONE], (it - 1) & 1, abort_flag, p.status, BWD_CODE(2, BB_ACC_DONE), p.bw.pipe_limit)) {
+                alive = false;
+                break;
+              }
+              mbar_arrive_expect_tx(&bars[BB_KV_FULL], 2 * BWD_TILE);
+              for (int h = 0; h < 2; ++h) {
+                tma_load_3d(smem + BWD_OFF_K + h * BWD_HALF, &tmK, &bars[BB_KV_FULL], h * 64, I.kv0, I.slab);
+                tma_load_3d(smem + BWD_OFF_V + h * BWD_HALF, &tmV, &bars[BB_KV_FULL], h * 64, I.kv0, I.slab);
+              }
+              ++kv_loads;
+            }
           }
-          if (!mbar_wait(&bars[BB_Q_EMPTY + s], ph ^ 1, abort_flag, p.status, BWD_CODE(2, BB_Q_EMPTY), p.bw.pipe_limit)) break;
-          uint8_t* dstq = smem + BWD_OFF_Q + s * 2 * BWD_TILE;
-          mbar_arrive_expect_tx(&bars[BB_Q_FULL + s], 2 * BWD_TILE);
-          for (int h = 0; h < 2; ++h) {
-            tma_load_3d(dstq + h * BWD_HALF, &tmQ, &bars[BB_Q_FULL + s], h * 64, y, qslab);
-            tma_load_3d(dstq + BWD_TILE + h * BWD_HALF, &tmDO, &bars[BB_Q_FULL + s], h * 64, y, qslab);
-          }
-          issued = j + 1;
+          ++it;
+          jj0 += ntot;
         }
-        if (*abort_flag) {
+        if (*abort_flag) {      // let the copies in flight land before the CTA's shared memory goes away
           auto drain = [&](uint64_t* bar, uint32_t ph) {
             const long long t0 = clock64();
             while (!mbar_try_wait(bar, ph) && clock64() - t0 < LVX_SPIN_LIMIT_CYCLES) {}
           };
-          drain(&bars[BB_KV_FULL], 0);
-          for (int j = max(0, issued - BWD_NSQ); j < issued; ++j) drain(&bars[BB_Q_FULL + j % BWD_NSQ], (j / BWD_NSQ) & 1);
+          if (kv_loads > 0) drain(&bars[BB_KV_FULL], (kv_loads - 1) & 1);
+          for (int jj = max(0, issued - BWD_NSQ); jj < issued; ++jj) drain(&bars[BB_Q_FULL + jj % BWD_NSQ], (jj / BWD_NSQ) & 1);
         }
       }
     } else {
@@ -467,78 +541,77 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                         umma_desc_join(ds_lo + ((kk * 2048) >> 4), HI), IDESC_DQ, kk > 0);
         };
 
-        bool ok = mbar_wait(&bars[BB_KV_FULL], 0, abort_flag, p.status, BWD_CODE(3, BB_KV_FULL), p.bw.pipe_limit);
-        ok = ok && mbar_wait(&bars[BB_Q_FULL + 0], 0, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL), p.bw.pipe_limit);
-        if (ok) {
-          tc_fence_after();
-          issue_st(tmem_base + TM_X, sK, sQ0);
-          tc_commit(&bars[BB_S_FULL]);
-          issue_st(tmem_base + TM_Y, sV, sQ0 + BWD_TILE);
-          tc_commit(&bars[BB_DP_FULL]);
-        }
-        for (int j = 0; ok && j < ntot; ++j) {
-          const int s = j % BWD_NSQ;
-          const uint32_t sQ = sQ0 + s * 2 * BWD_TILE, sDO = sQ + BWD_TILE;
-          BWD_TS(1, 0);
-          // dV needs P^T only, which is published before the dS^T half of the elementwise work; once dV has
-          // read X, S^T of the next tile can go there, i.e. while the warps are still producing dS^T
-          ok = mbar_wait(&bars[BB_P_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_P_FULL), p.bw.pipe_limit);
+        bool ok = true;
+        int it = 0, jj0 = 0;
+        for (int w = blockIdx.x; ok && w < p.nitems; w += gridDim.x) {
+          const Item I = item_of(w);
+          if (!I.live) continue;
+          // The item's first S^T and dP^T. X is free (the tensor pipe runs in order behind the last dV); Y still
+          // holds the previous item's last dQ^T until the drain warps have taken it.
+          ok = mbar_wait(&bars[BB_KV_FULL], it & 1, abort_flag, p.status, BWD_CODE(3, BB_KV_FULL), p.bw.pipe_limit);
+          ok = ok && mbar_wait(&bars[BB_Q_FULL + jj0 % BWD_NSQ], (jj0 / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL), p.bw.pipe_limit);
+          if (ok && jj0 > 0)
+            ok = mbar_wait(&bars[BB_DQ_FREE], (jj0 - 1) & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE), p.bw.pipe_limit);
           if (!ok) break;
           tc_fence_after();
-          issue_acc(tmem_base + TM_DV, tmem_base + TM_X, sDO, j == 0);
-          BWD_TS(1, 1);
-          const int s1 = (j + 1) % BWD_NSQ;
-          const uint32_t sQ1 = sQ0 + s1 * 2 * BWD_TILE;
-          if (j + 1 < ntot) {
-            ok = mbar_wait(&bars[BB_Q_FULL + s1], ((j + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL), p.bw.pipe_limit);
-            if (!ok) break;
-            tc_fence_after();
-            issue_st(tmem_base + TM_X, sK, sQ1);
+          {
+            const uint32_t sQf = sQ0 + (jj0 % BWD_NSQ) * 2 * BWD_TILE;
+            issue_st(tmem_base + TM_X, sK, sQf);
             tc_commit(&bars[BB_S_FULL]);
-            BWD_TS(1, 2);
+            issue_st(tmem_base + TM_Y, sV, sQf + BWD_TILE);
+            tc_commit(&bars[BB_DP_FULL]);
           }
-          ok = mbar_wait(&bars[BB_PDS_FULL], j & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL), p.bw.pipe_limit);
-          if (!ok) break;
-          tc_fence_after();
-          BWD_TS(1, 3);
-          issue_dq();                                   // Y: every warp took dP^T out before publishing dS^T
-          tc_commit(&bars[BB_DQ_FULL]);
-          issue_dk(sQ, j == 0);
-          tc_commit(&bars[BB_Q_EMPTY + s]);
-          tc_commit(&bars[BB_DS_FREE]);
-          BWD_TS(1, 4);
-          if (j + 1 < ntot) {
-            ok = mbar_wait(&bars[BB_DQ_FREE], j & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE), p.bw.pipe_limit);
+          for (int j = 0; ok && j < ntot; ++j) {
+            const int jj = jj0 + j;
+            const int s = jj % BWD_NSQ;
+            const uint32_t sQ = sQ0 + s * 2 * BWD_TILE, sDO = sQ + BWD_TILE;
+            BWD_TS(1, 0);
+            // dV needs P^T only, which is published before the dS^T half of the elementwise work; once dV has
+            // read X, S^T of the next tile can go there, i.e. while the warps are still producing dS^T
+            ok = mbar_wait(&bars[BB_P_FULL], jj & 1, abort_flag, p.status, BWD_CODE(3, BB_P_FULL), p.bw.pipe_limit);
             if (!ok) break;
             tc_fence_after();
-            BWD_TS(1, 5);
-            issue_st(tmem_base + TM_Y, sV, sQ1 + BWD_TILE);
-            tc_commit(&bars[BB_DP_FULL]);
-            BWD_TS(1, 6);
+            issue_acc(tmem_base + TM_DV, tmem_base + TM_X, sDO, j == 0);
+            BWD_TS(1, 1);
+            const int s1 = (jj + 1) % BWD_NSQ;
+            const uint32_t sQ1 = sQ0 + s1 * 2 * BWD_TILE;
+            if (j + 1 < ntot) {
+              ok = mbar_wait(&bars[BB_Q_FULL + s1], ((jj + 1) / BWD_NSQ) & 1, abort_flag, p.status, BWD_CODE(3, BB_Q_FULL), p.bw.pipe_limit);
+              if (!ok) break;
+              tc_fence_after();
+              issue_st(tmem_base + TM_X, sK, sQ1);
+              tc_commit(&bars[BB_S_FULL]);
+              BWD_TS(1, 2);
+            }
+            ok = mbar_wait(&bars[BB_PDS_FULL], jj & 1, abort_flag, p.status, BWD_CODE(3, BB_PDS_FULL), p.bw.pipe_limit);
+            if (!ok) break;
+            tc_fence_after();
+            BWD_TS(1, 3);
+            issue_dq();                                   // Y: every warp took dP^T out before publishing dS^T
+            tc_commit(&bars[BB_DQ_FULL]);
+            issue_dk(sQ, j == 0);
+            tc_commit(&bars[BB_Q_EMPTY + s]);
+            tc_commit(&bars[BB_DS_FREE]);
+            BWD_TS(1, 4);
+            if (j + 1 < ntot) {
+              ok = mbar_wait(&bars[BB_DQ_FREE], jj & 1, abort_flag, p.status, BWD_CODE(3, BB_DQ_FREE), p.bw.pipe_limit);
+              if (!ok) break;
+              tc_fence_after();
+              BWD_TS(1, 5);
+              issue_st(tmem_base + TM_Y, sV, sQ1 + BWD_TILE);
+              tc_commit(&bars[BB_DP_FULL]);
+              BWD_TS(1, 6);
+            }
           }
+          if (ok) tc_commit(&bars[BB_ACC_DONE]);
+          ++it;
+          jj0 += ntot;
         }
-        if (ok) {
-          tc_commit(&bars[BB_ACC_DONE]);
-        } else {
+        if (!ok) {
           tc_commit(&bars[BB_DRAIN]);
           const long long t0 = clock64();
           while (!mbar_try_wait(&bars[BB_DRAIN], 0) && clock64() - t0 < LVX_SPIN_LIMIT_CYCLES) {}
         }
-      }
-    }
-  } else if (!poisoned && p.accumulate != 1 && warp < 8) {
-    // No valid K/V row in this tile: its gradients are zero.
-    const int r = tid & 127;
-    if (kv0 + r < p.skv) {
-      const size_t off = (size_t(slab) * p.skv + kv0 + r) * 128;
-      float* base = warp < 4 ? p.dk_acc : p.dv_acc;
-      if (p.accumulate == 2) {
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(base) + off);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) reinterpret_cast<float4*>(base + off)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
   }
@@ -546,6 +619,20 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
   tc_fence_before();
   __syncthreads();
   if (warp == BWD_WARP_MMA) tmem_dealloc(tmem_base, 512);
+}
+
+// SMs of the current device (one process drives one GPU; looked up once).
+static int bwd_num_sms() {
+  static int n_sms = 0;
+  if (!n_sms) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      n_sms = n;
+    else
+      n_sms = 148;
+  }
+  return n_sms;
 }
 
 int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const float* lse, const float* delta,
@@ -589,7 +676,9 @@ int launch_bwd_block(const lvx_shape& s, const void* q, const void* d_o, const f
   p.status = status;
   p.bw = make_block_wait(bw, qb);
 
-  dim3 grid((s.Skv + 127) / 128, s.B * s.Hkv, 1);
+  p.kv_tiles = (s.Skv + 127) / 128;
+  p.nitems = p.kv_tiles * p.kv_slabs;
+  dim3 grid(std::min(p.nitems, bwd_num_sms()), 1, 1);      // persistent: one CTA per SM
   cudaError_t e = cudaSuccess;
   auto go = [&](auto kern) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);

@@ -73,6 +73,36 @@ def test_bwd_accumulate_over_steps(cuda_device):
     check(*run_case(cuda_device, 1, 8, 2, 256, 1024, torch.bfloat16, seed=9, two_steps=True), label="bwd_two_steps")
 
 
+@pytest.mark.parametrize("case", [
+    (1, 1, 1, 64, 128 * 300, None),                 # one query tile per K/V tile: every barrier phase flips per item
+    (2, 2, 2, 320, 128 * 120, [128 * 120, 7000]),   # three query tiles per item; 65 tiles of batch entry 1 hold no valid key
+    (1, 4, 2, 96, 128 * 200 + 37, None),            # ragged last K/V tile at the end of a CTA's walk
+])
+@pytest.mark.parametrize("final_dtype", [False, True])
+def test_bwd_many_items_per_cta(cuda_device, case, final_dtype):
+    """The grid is persistent (one CTA per SM), so with more K/V tiles than SMs a CTA walks several of them back to
+    back, some of them without any valid key. dK/dV in fp32 and written directly in the input dtype."""
+    from lv_xattn_b200 import ops, _lib
+    B, Hq, Hkv, Sq, Skv, valid = case
+    if not final_dtype:
+        check(*run_case(cuda_device, B, Hq, Hkv, Sq, Skv, torch.bfloat16, seed=13, kv_valid=valid), label=f"bwd_items{case}")
+        return
+    q, k, v, do = orc.make_inputs(B, Hq, Hkv, Sq, Skv, 128, 13, torch.bfloat16)
+    ref = orc.attention_fwd_bwd(q, k, v, do, SCALE, valid)
+    d = cuda_device
+    qd, kd, vd, dod = q.to(d), k.to(d), v.to(d), do.to(d)
+    kvl = None if valid is None else torch.tensor(valid, dtype=torch.int32, device=d)
+    o, lse = ops.fwd_block(qd, kd, vd, SCALE, kv_valid_len=kvl)
+    delta = ops.bwd_prep(o, dod)
+    dq = torch.zeros(B, Hq, Sq, 128, dtype=torch.float32, device=d)
+    dk = torch.full((B, Hkv, Skv, 128), float("nan"), dtype=torch.bfloat16, device=d)
+    dv = torch.full((B, Hkv, Skv, 128), float("nan"), dtype=torch.bfloat16, device=d)
+    ops.bwd_block(qd, dod, lse, delta, kd, vd, SCALE, dq, dk, dv, "final", kvl)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    check((dq.cpu(), dk.float().cpu(), dv.float().cpu()), ref[2:], label=f"bwd_items_final{case}")
+
+
 def test_bwd_run_twice(cuda_device):
     """dK/dV are accumulated in TMEM by one CTA per K/V tile in a fixed order: two runs agree bit for bit. dQ is
     reduce-added in fp32 by all K/V tiles in whatever order they finish, so two runs differ by fp32

@@ -59,6 +59,8 @@ class HostStreamedAttention:
         self._drained = {}        # output buffer name -> event: its device->host copy has finished
         self._last = None         # event: every copy queued so far on the output stream has finished
         self._kvl = {}            # (valid lengths, chunk bounds) -> per-chunk valid-length tensors
+        self._steps = 0           # the dK/dV output buffers alternate between two sets by step parity, so that a
+                                  # step's backward does not wait for the previous step's gradients to drain
 
     # ---- buffers and ordering -------------------------------------------------------------------------
     def _buf(self, name, shape, dtype):
@@ -213,10 +215,12 @@ class HostStreamedAttention:
         delta = ops.bwd_prep(o, s.do)
         dq_acc = self._buf("dq_acc", (B, Hq, Sq, D), torch.float32)
         dq_acc.zero_()
+        par = self._steps & 1
+        self._steps += 1
         for i, (c0, c1) in enumerate(bounds):
-            dkc = self._buf(f"dk{i}", (B, Hkv, c1 - c0, D), dt)
-            dvc = self._buf(f"dv{i}", (B, Hkv, c1 - c0, D), dt)
-            self._before_write(f"dkv{i}", main)
+            dkc = self._buf(f"dk{par}_{i}", (B, Hkv, c1 - c0, D), dt)
+            dvc = self._buf(f"dv{par}_{i}", (B, Hkv, c1 - c0, D), dt)
+            self._before_write(f"dkv{par}_{i}", main)
             ops.bwd_block(s.q, s.do, lse, delta, s.k[i], s.v[i], sm_scale, dq_acc, dkc, dvc, "final", kvl[i])
             ev = torch.cuda.Event()
             ev.record(main)
@@ -225,7 +229,7 @@ class HostStreamedAttention:
             else:
                 pairs = [(out[b, h, c0:c1], src[b, h]) for b in range(B) for h in range(Hkv)
                          for out, src in ((out_dk, dkc), (out_dv, dvc))]
-            self._drain(pairs, ev, [f"dkv{i}"])
+            self._drain(pairs, ev, [f"dkv{par}_{i}"])
         self._before_write("dq", main)
         dq = ops.add_cast(dq_acc, None, dt, out=self._buf("dq", (B, Hq, Sq, D), dt))
         ev = torch.cuda.Event()

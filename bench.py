@@ -881,8 +881,9 @@ def main():
                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e_steps,
                "latency_ms_per_step": lat_ms,
                "overlap": "consecutive steps pipelined over two device-side input sets, "
-                          f"{args.e2e_pipeline_chunks} K/V chunk(s) per step; latency_ms_per_step is one step alone, "
-                          f"its K/V streamed in {args.e2e_chunks} chunks"}
+                          + (f"{args.e2e_pipeline_chunks} K/V chunk(s) per step; latency_ms_per_step is one step alone, "
+                             f"its K/V streamed in {args.e2e_chunks} chunks" if world == 1 else
+                             "each rank's whole shard per step; latency_ms_per_step is one step alone")}
 
     # ---- CPU baseline (rank 0, N=1 only) ----------------------------------------------------------------
     cpu = None

@@ -185,7 +185,7 @@ fp32_fwd_kernel(const Fp32FwdParams p) {
       for (int c = 0; c < 8; ++c) o[i][c] *= alpha;
     }
     __syncthreads();
-#pragma unroll 1
+#pragma unroll 2
     for (int j = 0; j < SM_T; j += 4) {
       float4 pr[4];
 #pragma unroll
@@ -277,7 +277,7 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) s[i][j] = dp[i][j] = 0.f;
-#pragma unroll 1
+#pragma unroll 2
       for (int d = 0; d < 128; d += 4) {
         float4 a[4], b[4];
 #pragma unroll
@@ -322,7 +322,7 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
     __syncthreads();
     // dV[kv][d] += sum_q P[q][kv] dO[q][d];  dK[kv][d] += sum_q dS[q][kv] Q[q][d]
     // (this thread: key rows 4*ty+i -- one 16-byte piece of a P / dS row -- and columns 4*tx+64*h+e)
-#pragma unroll 2
+#pragma unroll 4
     for (int qi = 0; qi < SM_T; ++qi) {
       const float4 pr = ld4(sP + qi * SM_LDP + 4 * ty);
       const float4 dsr = ld4(sDS + qi * SM_LDP + 4 * ty);
@@ -342,7 +342,7 @@ fp32_bwd_kernel(const Fp32BwdParams p) {
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int c = 0; c < 8; ++c) dq[i][c] = 0.f;
-#pragma unroll 1
+#pragma unroll 2
     for (int j = 0; j < SM_T; j += 4) {
       float4 dsr[4];
 #pragma unroll
